@@ -37,13 +37,35 @@ constexpr int NACC = (VD + 7) / 8;             // output dims per thread
 constexpr int QS = HD + 1, KS = HD + 1, PS = KC + 1;
 constexpr size_t SMEM_FLOATS = (size_t)QT * QS + (size_t)KC * KS + (size_t)KC * VD + (size_t)QT * PS;
 
-template <typename T>
+// What mixers beyond plain grouped-query attention ask for.
+//   softcap > 0      score <- softcap * tanh(score / softcap), after the scale
+//   sink_values      with `sink`: the exponent of the term the denominator holds besides the keys', one per
+//                    query head (null: 0 for every head)
+//   maps >= 1        attention maps a head: the query heads come as [head][map], the key heads as
+//                    [kv head][map], and the maps of a head share the values of kv head = head / (heads / kv heads).
+//                    Hq counts query heads with their maps, Hkv the value heads; the cache holds Hkv * maps key heads.
+//   value_in_key     the value of a key is its own first VD channels; the cache holds keys only
+struct Extra {
+    float softcap;
+    const float* sink_values;
+    int maps;
+    int value_in_key;
+};
+
+// key head and value head of query head h
+__device__ __forceinline__ void heads_of(int h, int Hq, int Hkv, int maps, int& key_head, int& value_head) {
+    const int per = Hq / (Hkv * maps);                   // heads (each of `maps` maps) a kv head
+    value_head = (h / maps) / per;
+    key_head = value_head * maps + h % maps;
+}
+
+template <typename T, typename TO>
 __global__ void __launch_bounds__(THREADS)
-attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+attention_plain_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ out, int out_stride,
                        const T* __restrict__ cache, const int* __restrict__ block_table,
                        int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                        const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
-                       int Hq, int Hkv, int page_size, float scale, int window, int block, int sink) {
+                       int Hq, int Hkv, int page_size, float scale, int window, int block, int sink, Extra ex) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -59,7 +81,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     const int q_begin = cu_q[b], q_len = cu_q[b + 1] - q_begin;
     const int kvl = kv_len[b];
     const int pos0 = kvl - q_len;                        // position of the entry's first token
-    const int g = h / (Hq / Hkv);
+    int kh, g;                                           // key head, value head
+    heads_of(h, Hq, Hkv, ex.maps, kh, g);
     const int tid = threadIdx.x;
     const int row = tid >> 3, l8 = tid & 7;
     const int rows_here = min(QT, q_len - j0);
@@ -82,16 +105,19 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
 
     // with a sink the sums start from a key of score 0 that has no value: maximum 0, sum exp(0 - 0) = 1
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    // (with sink values: a term exp(sink_h) instead, so the maximum starts at sink_h)
+    float m = sink ? (ex.sink_values ? ex.sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
 
     const int* bt = block_table + (size_t)b * table_stride;
     // a page: keys [kv head][slot][HD], then values [kv head][slot][VD]
-    const size_t page_elems = (size_t)Hkv * page_size * (HD + VD);
-    const size_t v_base = (size_t)Hkv * page_size * HD + (size_t)g * page_size * VD;
-    const size_t k_base = (size_t)g * page_size * HD;
+    const int Hk = Hkv * ex.maps;
+    const size_t page_elems = (size_t)page_size * ((size_t)Hk * HD + (ex.value_in_key ? 0 : (size_t)Hkv * VD));
+    const size_t k_base = (size_t)kh * page_size * HD;
+    const size_t v_base = ex.value_in_key ? k_base : (size_t)Hk * page_size * HD + (size_t)g * page_size * VD;
+    const int v_row = ex.value_in_key ? HD : VD;         // elements from one key's value to the next
     for (int kb = (lo_tile / KC) * KC; kb <= p_last; kb += KC) {
         __syncthreads();                                 // previous chunk's Vs/Ps reads are done
         // a warp a key: the page is looked up once per key and the lanes read along the head
@@ -105,7 +131,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                 const size_t page = (size_t)bt[blk] * page_elems;
                 const int off = key - blk * page_size;
                 kp = cache + page + k_base + (size_t)off * HD;
-                vp = cache + page + v_base + (size_t)off * VD;
+                vp = cache + page + v_base + (size_t)off * v_row;
             }
             for (int d = tid & 31; d < HD; d += 32) Ks[kk * KS + d] = seen ? to_f32<T>(kp[d]) : 0.f;
             for (int d = tid & 31; d < VD; d += 32) Vs[kk * VD + d] = seen ? to_f32<T>(vp[d]) : 0.f;
@@ -124,7 +150,9 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
 #pragma unroll 8
             for (int d = 0; d < HD; ++d) dot = fmaf(qr[d], kr[d], dot);
             const bool seen = row_valid && key <= p_row && key >= lo_row;
-            s[c] = seen ? dot * scale : -INFINITY;
+            float sc = dot * scale;
+            if (ex.softcap > 0.f) sc = ex.softcap * tanhf(sc / ex.softcap);
+            s[c] = seen ? sc : -INFINITY;
             cmax = fmaxf(cmax, s[c]);
         }
 #pragma unroll
@@ -161,10 +189,10 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
     }
     if (row_valid) {
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* o = out + (size_t)(q_begin + j0 + row) * out_stride + (size_t)h * VD + l8;
+        TO* o = out + (size_t)(q_begin + j0 + row) * out_stride + (size_t)h * VD + l8;
 #pragma unroll
         for (int i = 0; i < NACC; ++i)
-            if (VD % 8 == 0 || l8 + 8 * i < VD) o[8 * i] = from_f32<T>(acc[i] * inv);
+            if (VD % 8 == 0 || l8 + 8 * i < VD) o[8 * i] = from_f32<TO>(acc[i] * inv);
     }
 }
 
@@ -192,24 +220,27 @@ constexpr size_t SINGLE_SMEM_FLOATS = (size_t)SG * HD + (size_t)SG * SK + 3 * SG
 // thread owns one 16-byte piece of the value row and every (THREADS / pieces)-th key, so that one load serves
 // 8 (bf16) channels of all heads and 128 loads are in flight a CTA instead of 16; the threads' parts are added
 // in a fixed order at the end.
-template <typename T, int GM>
+template <typename T, typename TO, int GM>
 __global__ void __launch_bounds__(THREADS)
-attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+attention_single_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ out, int out_stride,
                         const T* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                         const int* __restrict__ entry_list, int Hq, int Hkv, int page_size, float scale,
-                        int window, int block, int sink, float* __restrict__ part) {
+                        int window, int block, int sink, float* __restrict__ part, Extra ex) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
-    const int G = Hq / Hkv;
+    const int Hk = Hkv * ex.maps;                        // key heads: a CTA each
+    const int G = Hq / Hk;                               // query heads that read this CTA's key head
     float* qs = smem;                                    // [G][HD]
     float* sc = qs + SG * HD;                            // [G][SK]
     float* mrun = sc + SG * SK;                          // [G] running maximum
     float* lrun = mrun + SG;                             // [G] running sum
     float* arun = lrun + SG;                             // [G] what the chunk rescales the old sums by
     float* red = arun + SG;                              // [warps][G][VD]
-    const int kvh = blockIdx.x;
+    const int kh = blockIdx.x, kvh = kh / ex.maps, mp = kh - kvh * ex.maps;
+    // the g-th of them is query head (kvh * G + g) * maps + mp
+    const int head0 = kvh * G * ex.maps + mp, head_step = ex.maps;
     const int b = entry_list[blockIdx.y];
     if (b < 0) return;
     const int t = cu_q[b];
@@ -227,9 +258,14 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     constexpr int WARPS = THREADS / 32;
-    for (int e = tid; e < G * HD; e += THREADS)
-        qs[e] = to_f32<T>(q[(size_t)t * q_stride + (size_t)kvh * G * HD + e]);
-    if (tid < G) { mrun[tid] = sink ? 0.f : -INFINITY; lrun[tid] = sink ? 1.f : 0.f; }
+    for (int e = tid; e < G * HD; e += THREADS) {
+        const int g = e / HD;
+        qs[e] = to_f32<T>(q[(size_t)t * q_stride + (size_t)(head0 + g * head_step) * HD + (e - g * HD)]);
+    }
+    if (tid < G) {
+        mrun[tid] = sink ? (ex.sink_values ? ex.sink_values[head0 + tid * head_step] : 0.f) : -INFINITY;
+        lrun[tid] = sink ? 1.f : 0.f;
+    }
     constexpr int VECW = 16 / (int)sizeof(T);               // elements of a 16-byte piece
     constexpr int PIECES = VD % VECW == 0 ? VD / VECW : 1;  // pieces of a value row
     constexpr bool WIDE_OK = GM <= 8 && VD % VECW == 0 && THREADS % PIECES == 0 && PIECES <= THREADS;
@@ -245,11 +281,12 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll
         for (int i = 0; i < VECW; ++i) accw[g][i] = 0.f;
     const int* bt = block_table + (size_t)b * table_stride;
-    const size_t page_elems = (size_t)Hkv * page_size * (HD + VD);
-    const size_t v_base = (size_t)Hkv * page_size * HD + (size_t)kvh * page_size * VD;
-    const size_t k_base = (size_t)kvh * page_size * HD;
+    const size_t page_elems = (size_t)page_size * ((size_t)Hk * HD + (ex.value_in_key ? 0 : (size_t)Hkv * VD));
+    const size_t k_base = (size_t)kh * page_size * HD;
+    const size_t v_base = ex.value_in_key ? k_base : (size_t)Hk * page_size * HD + (size_t)kvh * page_size * VD;
+    const int v_row = ex.value_in_key ? HD : VD;         // elements from one key's value to the next
     // value rows start on 16-byte boundaries (the cache itself does: the host checks)
-    const bool wide = WIDE_OK && page_elems % VECW == 0 && v_base % VECW == 0;
+    const bool wide = WIDE_OK && page_elems % VECW == 0 && v_base % VECW == 0 && v_row % VECW == 0;
     const int piece = tid % PIECES, kgroup = tid / PIECES;
     __syncthreads();
     for (int k0 = lo; k0 <= p; k0 += SK) {
@@ -294,7 +331,10 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
             }
 #pragma unroll
             for (int g = 0; g < SG; ++g)
-                if (g < G) sc[g * SK + kk] = s[g] * scale;
+                if (g < G) {
+                    const float x = s[g] * scale;
+                    sc[g * SK + kk] = ex.softcap > 0.f ? ex.softcap * tanhf(x / ex.softcap) : x;
+                }
         }
         __syncthreads();
         // the chunk's maximum, the weights and their sum: a warp a head
@@ -332,7 +372,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll 4                                          // the loads of four keys in flight a thread
             for (int kk = kgroup; kk < n; kk += KG) {
                 const int key = k0 + kk, blk = key / page_size;
-                const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD + piece * VECW;
+                const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * v_row + piece * VECW;
                 const uint4 raw = *reinterpret_cast<const uint4*>(vp);
                 const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
@@ -356,7 +396,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 #pragma unroll 4                                          // the loads of four keys in flight
                 for (int kk = warp; kk < n; kk += WARPS) {
                     const int key = k0 + kk, blk = key / page_size;
-                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD;
+                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * v_row;
                     float v[SV];
 #pragma unroll
                     for (int i = 0; i < SV; ++i) v[i] = lane + 32 * i < VD ? to_f32<T>(vp[lane + 32 * i]) : 0.f;
@@ -373,7 +413,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
                 // piece still, element by element
                 for (int kk = kgroup; kk < n; kk += KG) {
                     const int key = k0 + kk, blk = key / page_size;
-                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * VD + piece * VECW;
+                    const T* vp = cache + (size_t)bt[blk] * page_elems + v_base + (size_t)(key - blk * page_size) * v_row + piece * VECW;
 #pragma unroll
                     for (int g = 0; g < (WIDE_OK ? GM : 1); ++g)
                         if (g < G) {
@@ -414,11 +454,11 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
         }
         const float l = lrun[g];
         if (splits > 1) {
-            float* dst = part + (((size_t)blockIdx.y * Hq + kvh * G + g) * splits + blockIdx.z) * (VD + 2);
+            float* dst = part + (((size_t)blockIdx.y * Hq + head0 + g * head_step) * splits + blockIdx.z) * (VD + 2);
             dst[d] = total;
             if (d == 0) { dst[VD] = mrun[g]; dst[VD + 1] = l; }
         } else {
-            out[(size_t)t * out_stride + (size_t)(kvh * G + g) * VD + d] = from_f32<T>(l > 0.f ? total / l : 0.f);
+            out[(size_t)t * out_stride + (size_t)(head0 + g * head_step) * VD + d] = from_f32<TO>(l > 0.f ? total / l : 0.f);
         }
     }
 }
@@ -429,7 +469,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ o
 template <typename T>
 __global__ void attention_single_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
                                               const int* __restrict__ cu_q, const int* __restrict__ entry_list,
-                                              int Hq, int splits, int sink) {
+                                              int Hq, int splits, int sink, const float* __restrict__ sink_values) {
     pdl_trigger();
     pdl_wait();
     const int b = entry_list[blockIdx.y], h = blockIdx.x;
@@ -437,9 +477,10 @@ __global__ void attention_single_merge_kernel(const float* __restrict__ part, T*
     const int t = cu_q[b];
     if (cu_q[b + 1] - t != 1) return;
     const float* src = part + ((size_t)blockIdx.y * Hq + h) * splits * (VD + 2);
-    float M = sink ? 0.f : -INFINITY;
+    const float sv = sink && sink_values ? sink_values[h] : 0.f;    // the sink's exponent
+    float M = sink ? sv : -INFINITY;
     for (int z = 0; z < splits; ++z) M = fmaxf(M, src[(size_t)z * (VD + 2) + VD]);
-    float L = sink ? expf(-M) : 0.f;
+    float L = sink ? expf(sv - M) : 0.f;
     for (int z = 0; z < splits; ++z) {
         const float m = src[(size_t)z * (VD + 2) + VD];
         if (m != -INFINITY) L += src[(size_t)z * (VD + 2) + VD + 1] * expf(m - M);
@@ -454,24 +495,28 @@ __global__ void attention_single_merge_kernel(const float* __restrict__ part, T*
     }
 }
 
-template <typename T>
+template <typename T, typename TO>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* cache,
            const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
            const int* tile_entry, const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
-           float scale, int window, int block, int sink, cudaStream_t s) {
+           float scale, int window, int block, int sink, Extra ex, cudaStream_t s) {
     static bool configured = false;
     const size_t smem = SMEM_FLOATS * sizeof(float);
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_plain_kernel<T>,
+        cudaError_t e = cudaFuncSetAttribute(attention_plain_kernel<T, TO>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(n_tiles, Hq);
-    RI_CHECKED(ri_launch(attention_plain_kernel<T>, dim3(grid), dim3(THREADS), smem, s, 
-        (const T*)q, q_stride, (T*)out, out_stride, (const T*)cache, block_table, table_stride,
-        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window, block, sink));
+    RI_CHECKED(ri_launch(attention_plain_kernel<T, TO>, dim3(grid), dim3(THREADS), smem, s,
+        (const T*)q, q_stride, (TO*)out, out_stride, (const T*)cache, block_table, table_stride,
+        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window, block, sink, ex));
     return ri_launch_status();
+}
+
+bool extra_fits(int Hq, int Hkv, const Extra& ex) {
+    return Hkv > 0 && ex.maps >= 1 && Hq % (Hkv * ex.maps) == 0 && (!ex.value_in_key || (VD <= HD && ex.maps == 1 && Hkv >= 1));
 }
 }  // namespace
 
@@ -484,55 +529,83 @@ RI_API int ri_attention_plain_tile_rows() { return QT; }
 // [kv head][slot][VD] ([page][K|V][kv head][slot][HD] when the two sizes are equal).  tile_entry[i] = batch entry of tile i
 // (-1: skip), tile_q0[i] = its first query row within that entry.  sink: the softmax's denominator has one
 // added, p_j = exp(s_j) / (1 + sum exp(s_j)): a key of score 0 that carries no value.
+// The same with the options of `Extra` (see there) and, with out_f32, an fp32 `out` whatever the cache's dtype.
+RI_API int ri_attention_plain_ex(const void* q, int q_stride, void* out, int out_stride,
+                                 const void* cache, int dtype, const int* block_table, int table_stride,
+                                 const int* cu_q, const int* kv_len, const int* tile_entry,
+                                 const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
+                                 float scale, int window, int block, int sink, float softcap,
+                                 const float* sink_values, int maps, int value_in_key, int out_f32, void* stream) {
+    if (n_tiles <= 0) return 0;
+    const Extra ex{softcap, sink_values, maps, value_in_key};
+    if (!extra_fits(Hq, Hkv, ex)) return (int)cudaErrorInvalidValue;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RI_BF16 && out_f32)
+        return launch<bf16, float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
+                                   kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, ex, s);
+    if (dtype == RI_BF16)
+        return launch<bf16, bf16>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
+                                  kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, ex, s);
+    return launch<float, float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
+                                kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, ex, s);
+}
+
 RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_stride,
                               const void* cache, int dtype, const int* block_table, int table_stride,
                               const int* cu_q, const int* kv_len, const int* tile_entry,
                               const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
                               float scale, int window, int block, int sink, void* stream) {
-    if (n_tiles <= 0) return 0;
-    if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == RI_BF16)
-        return launch<bf16>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                            kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, s);
-    return launch<float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
-                         kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink, s);
+    return ri_attention_plain_ex(q, q_stride, out, out_stride, cache, dtype, block_table, table_stride, cu_q, kv_len,
+                                 tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink,
+                                 0.f, nullptr, 1, 0, 0, stream);
 }
 
 // Entries that bring a single token (entry_list[i], -1: skip): keys and values of a kv head are read once
 // for its query heads.  splits > 1: every entry's keys in that many ranges (a CTA each) through `part`, fp32
 // [n_entries][Hq][splits][VD + 2], and a second launch that joins them.  Returns cudaErrorNotSupported for more than 16 query heads a kv head or values
 // wider than 128 (the caller then uses the tiled kernel above, which takes everything).
-RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
-                               const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
-                               const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
-                               int window, int block, int sink, int splits, float* part, void* stream) {
+RI_API int ri_attention_single_ex(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
+                                  const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
+                                  const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
+                                  int window, int block, int sink, int splits, float* part, float softcap,
+                                  const float* sink_values, int maps, int value_in_key, int out_f32, void* stream) {
     if (n_entries <= 0) return 0;
-    if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
-    if (Hq / Hkv > SG || SV > 4) return (int)cudaErrorNotSupported;
+    const Extra ex{softcap, sink_values, maps, value_in_key};
+    if (!extra_fits(Hq, Hkv, ex)) return (int)cudaErrorInvalidValue;
+    if (Hq / (Hkv * maps) > SG || SV > 4) return (int)cudaErrorNotSupported;
     if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid(Hkv, n_entries, splits);
-#define RI_SINGLE(T) do { const int G_ = Hq / Hkv; \
-    if (G_ <= 4) RI_SINGLE_G(T, 4); else if (G_ <= 8) RI_SINGLE_G(T, 8); else RI_SINGLE_G(T, 16); } while (0)
-#define RI_SINGLE_G(T, GM) do { static bool configured = false; \
+    dim3 grid(Hkv * maps, n_entries, splits);
+#define RI_SINGLE(T, TO) do { const int G_ = Hq / (Hkv * maps); \
+    if (G_ <= 4) RI_SINGLE_G(T, TO, 4); else if (G_ <= 8) RI_SINGLE_G(T, TO, 8); else RI_SINGLE_G(T, TO, 16); } while (0)
+#define RI_SINGLE_G(T, TO, GM) do { static bool configured = false; \
     /* the parts' meeting place is as large as this many heads need: fewer heads, more CTAs an SM */ \
     const size_t wide_red = GM <= 8 ? (size_t)THREADS * GM * 8 : 0, old_red = (size_t)(THREADS / 32) * SG * VD; \
     const size_t smem = ((size_t)SG * HD + (size_t)SG * SK + 3 * SG + (wide_red > old_red ? wide_red : old_red)) * sizeof(float); \
     if (!configured) { \
-        cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        cudaError_t e = cudaFuncSetAttribute(attention_single_kernel<T, TO, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) return (int)e; \
         configured = true; } \
-    RI_CHECKED(ri_launch(attention_single_kernel<T, GM>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (T*)out, \
+    RI_CHECKED(ri_launch(attention_single_kernel<T, TO, GM>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (TO*)out, \
         out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
-        window, block, sink, part)); \
-    if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<T>, dim3(Hq, n_entries), dim3(VD < 64 ? 32 : 64), 0, s, \
-        (const float*)part, (T*)out, out_stride, cu_q, entry_list, Hq, splits, sink)); } while (0)
-    if (dtype == RI_BF16) RI_SINGLE(bf16);
-    else RI_SINGLE(float);
+        window, block, sink, part, ex)); \
+    if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<TO>, dim3(Hq, n_entries), dim3(VD < 64 ? 32 : 64), 0, s, \
+        (const float*)part, (TO*)out, out_stride, cu_q, entry_list, Hq, splits, sink, sink_values)); } while (0)
+    if (dtype == RI_BF16 && out_f32) RI_SINGLE(bf16, float);
+    else if (dtype == RI_BF16) RI_SINGLE(bf16, bf16);
+    else RI_SINGLE(float, float);
 #undef RI_SINGLE
 #undef RI_SINGLE_G
     return ri_launch_status();
+}
+
+RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_stride, const void* cache, int dtype,
+                               const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
+                               const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
+                               int window, int block, int sink, int splits, float* part, void* stream) {
+    return ri_attention_single_ex(q, q_stride, out, out_stride, cache, dtype, block_table, table_stride, cu_q, kv_len,
+                                  entry_list, n_entries, Hq, Hkv, page_size, scale, window, block, sink, splits, part,
+                                  0.f, nullptr, 1, 0, 0, stream);
 }
 
 RI_API int ri_attention_single_supports(int Hq, int Hkv) {

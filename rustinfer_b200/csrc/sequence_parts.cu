@@ -283,18 +283,33 @@ __global__ void gated_head_norm_kernel(const float* __restrict__ o, const TA* __
 }
 
 // --------------------------------------------------------------- element-wise activations
-// kind 0: gelu with erf; 1: tanh; 2: gelu with tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+// kind 0: gelu with erf; 1: tanh; 2: gelu with tanh, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)));
+// 3: the square of relu; 4: silu, z / (1 + exp(-z))
+__device__ __forceinline__ float activate(float z, int kind) {
+    if (kind == 0) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    if (kind == 1) return tanhf(z);
+    if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return z > 0.f ? z * z : 0.f;
+    return z / (1.0f + expf(-z));
+}
+
 template <typename TA>
 __global__ void activation_kernel(const TA* __restrict__ x, TA* __restrict__ out, long long n, int kind) {
     pdl_trigger();
     pdl_wait();
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-        const float z = to_f32<TA>(x[i]);
-        float y;
-        if (kind == 0) y = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
-        else if (kind == 1) y = tanhf(z);
-        else y = 0.5f * z * (1.0f + tanhf(0.79788456080286535588f * (z + 0.044715f * z * z * z)));
-        out[i] = from_f32<TA>(y);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TA>(activate(to_f32<TA>(x[i]), kind));
+}
+
+// the first `cols` columns of every row of x [rows][stride], in place
+template <typename TA>
+__global__ void activation_cols_kernel(TA* __restrict__ x, int stride, long long total, int cols, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols;
+        TA* p = x + r * stride + (i - r * cols);
+        *p = from_f32<TA>(activate(to_f32<TA>(*p), kind));
     }
 }
 
@@ -466,6 +481,17 @@ RI_API int ri_activation(const void* x, void* out, int act_dtype, long long n, i
         RI_CHECKED(ri_launch(activation_kernel<bf16>, dim3(ew_blocks(n)), dim3(256), 0, s, (const bf16*)x, (bf16*)out, n, kind));
     else
         RI_CHECKED(ri_launch(activation_kernel<float>, dim3(ew_blocks(n)), dim3(256), 0, s, (const float*)x, (float*)out, n, kind));
+    return ri_launch_status();
+}
+
+RI_API int ri_activation_cols(void* x, int act_dtype, int stride, int rows, int cols, int kind, void* stream) {
+    const long long total = (long long)rows * cols;
+    if (total <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == RI_BF16)
+        RI_CHECKED(ri_launch(activation_cols_kernel<bf16>, dim3(ew_blocks(total)), dim3(256), 0, s, (bf16*)x, stride, total, cols, kind));
+    else
+        RI_CHECKED(ri_launch(activation_cols_kernel<float>, dim3(ew_blocks(total)), dim3(256), 0, s, (float*)x, stride, total, cols, kind));
     return ri_launch_status();
 }
 

@@ -164,13 +164,15 @@ __global__ void hyper_collect_kernel(float* __restrict__ X, int fresh, const TY*
 // `rot` channels of every head of q and k (pairs (2i, 2i+1) when interleaved, else (i, i + rot/2)) by the
 // angles of cos/sin [positions][rot/2], store q rounded to the activation dtype and k, v into the pages of
 // `cache` at slot_of_token[t] (page*page_size + offset; < 0 or no cache: not stored).  One CTA a token.
+// Hv: heads of v where they are fewer than the heads of k (several attention maps, each with keys of
+// its own, over one set of values); a page then holds Hkv heads of keys and Hv heads of values.
 template <typename TI, typename TA, typename TW>
 __global__ void qkv_prepare_kernel(const TI* __restrict__ qkv, int row_stride, const float* __restrict__ bias,
                                    const TW* __restrict__ q_w, const TW* __restrict__ k_w, int norm_mode, float eps,
                                    const int* __restrict__ positions, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, int rot, int interleaved,
                                    const int* __restrict__ slot_of_token, TA* __restrict__ cache,
-                                   TA* __restrict__ q_out, int Hq, int Hkv, int dk, int dv, int has_kv, int page_size) {
+                                   TA* __restrict__ q_out, int Hq, int Hkv, int Hv, int dk, int dv, int has_kv, int page_size) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
@@ -229,14 +231,14 @@ __global__ void qkv_prepare_kernel(const TI* __restrict__ qkv, int row_stride, c
     if (!has_kv || !cache || !slot_of_token) return;
     const int slot = slot_of_token[t];
     if (slot < 0) return;
-    const size_t page_elems = (size_t)Hkv * page_size * (dk + dv);
+    const size_t page_elems = (size_t)page_size * ((size_t)Hkv * dk + (size_t)Hv * dv);
     TA* page = cache + (size_t)(slot / page_size) * page_elems;
     const int off = slot % page_size;
     for (int i = tid; i < nk; i += nth) {
         const int g = i / dk, c = i - g * dk;
         page[((size_t)g * page_size + off) * dk + c] = from_f32<TA>(ks[i]);
     }
-    const int nv = Hkv * dv;
+    const int nv = Hv * dv;
     TA* vpage = page + (size_t)Hkv * page_size * dk;
     for (int i = tid; i < nv; i += nth) {
         const int g = i / dv, c = i - g * dv;
@@ -298,8 +300,9 @@ RI_API int ri_qkv_prepare(const void* qkv, int in_dtype, int row_stride, const f
                           const void* k_w, int w_dtype, int norm_mode, float eps, const int* positions,
                           const float* cos_t, const float* sin_t, int rot, int interleaved, const int* slot_of_token,
                           void* cache, void* q_out, int act_dtype, int tokens, int Hq, int Hkv, int dk, int dv,
-                          int has_kv, int page_size, void* stream) {
+                          int has_kv, int page_size, int value_heads, void* stream) {
     if (tokens <= 0) return 0;
+    const int Hv = value_heads > 0 ? value_heads : Hkv;
     if (rot < 0 || rot > dk || (rot & 1) || (rot > 0 && (!cos_t || !sin_t || !positions))) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(Hq * dk + (has_kv ? Hkv * dk : 0) + 33) * sizeof(float);
@@ -312,7 +315,7 @@ RI_API int ri_qkv_prepare(const void* qkv, int in_dtype, int row_stride, const f
             configured = true; } \
         RI_CHECKED(ri_launch(qkv_prepare_kernel<TI, TA, TW>, dim3(tokens), dim3(256), smem, s, (const TI*)qkv, row_stride, bias, \
             (const TW*)q_w, (const TW*)k_w, norm_mode, eps, positions, cos_t, sin_t, rot, interleaved, slot_of_token, (TA*)cache, \
-            (TA*)q_out, Hq, Hkv, dk, dv, has_kv, page_size)); } while (0)
+            (TA*)q_out, Hq, Hkv, Hv, dk, dv, has_kv, page_size)); } while (0)
     if (act_dtype == RI_BF16) {
         if (in_dtype == RI_BF16) { if (w_dtype == RI_BF16) RI_QP(bf16, bf16, bf16); else RI_QP(bf16, bf16, float); }
         else { if (w_dtype == RI_BF16) RI_QP(float, bf16, bf16); else RI_QP(float, bf16, float); }

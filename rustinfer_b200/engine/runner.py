@@ -295,8 +295,7 @@ class ModelRunner:
         per_page = 0
         for g in self.layout.groups:
             if isinstance(g.need, PagedKV):
-                per_page += (len(g.entries) * g.need.num_kv_heads * self.page_size
-                             * (g.need.head_dim + g.need.v_dim) * esize)
+                per_page += len(g.entries) * self.page_size * g.need.elems_per_token() * esize
         cap = self.max_batch_seqs * self.max_pages_per_request
         if per_page == 0:
             return 1
@@ -314,11 +313,10 @@ class ModelRunner:
             n = len(g.entries)
             if isinstance(g.need, PagedKV):
                 self._paged_index[gi] = len(self._paged_index)
-                if g.need.v_dim == g.need.head_dim:
+                if g.need.plain:
                     shape = (n, self.num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim)
-                else:                           # a page's keys, then its values, which have another size
-                    shape = (n, self.num_pages,
-                             g.need.num_kv_heads * self.page_size * (g.need.head_dim + g.need.v_dim))
+                else:                           # a page's keys, then its values (of another size, fewer heads, or none)
+                    shape = (n, self.num_pages, self.page_size * g.need.elems_per_token())
                 t = torch.zeros(shape, dtype=self.dtype, device=self.device)
             elif isinstance(g.need, FixedState):
                 # one row more than there are slots: padding rows of a captured step point there

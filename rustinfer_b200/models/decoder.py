@@ -9,7 +9,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts import attention, experts, ffn, hyper, linear_attention, norm, parallel, rope, stem_tail  # noqa: F401  (registers the built-in parts)
+from ..parts import (attention, attention_variants, experts, ffn, hyper, linear_attention, norm, parallel, rope,  # noqa: F401
+                     stem_tail)  # (registers the built-in parts)
 from ..parts.base import EMBEDDINGS, HEADS, NORMS, BuildContext, CacheNeed, ParamDecl, StepContext, StepIndex
 from ..parts.block import Block, Hidden
 from ..parts.spec import ModelSpec

@@ -395,64 +395,83 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                     cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor,
                     tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: Optional[int], block: Optional[int] = None,
-                    value_dim: Optional[int] = None, sink: bool = False) -> None:
+                    value_dim: Optional[int] = None, sink: bool = False, softcap: Optional[float] = None,
+                    sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
     """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*vd].  `block`: a query
     sees only the keys of its own block of that many positions (counted from 0).  `value_dim`:
     size of a value where it is not the keys'; the cache is then [pages, Hkv*page*(hd+vd)].  `sink`:
-    the softmax's denominator has one added (a key of score 0 without a value)."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0)
+    the softmax's denominator has one added (a key of score 0 without a value); with `sink_values`
+    (fp32 [Hq]) it has exp(sink_values[h]) added instead.  `softcap` c: score <- c tanh(score / c).
+    `maps` m: every head has m attention maps with queries and keys of their own over one set of
+    values; `num_heads` counts query heads with their maps ([head][map]), `num_kv_heads` the value
+    heads, and the cache holds Hkv*m key heads ([kv head][map]).  `value_in_key`: a key's value is
+    its own first `value_dim` channels, and the cache holds keys only.  `out` may be fp32 whatever
+    the cache's dtype."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0, sink_values)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_q0, "tile_q0")):
         _i32(t, n)
-    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
-        raise KernelError("attention: q, out and cache share a dtype; q and out have unit column stride")
-    _contig(cache, "cache")
     vd = value_dim or head_dim
-    page_size = paged_cache_page_size(cache, num_kv_heads, head_dim, vd)
-    if num_heads % num_kv_heads:
-        raise KernelError("attention: heads must be a multiple of kv heads")
+    page_size = _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key)
     lib = L.attention_plain(head_dim, vd)
-    check(lib.ri_attention_plain(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache),
-                                 dtype_code(cache.dtype), _p(block_table), block_table.stride(0),
-                                 _p(cu_q), _p(kv_len), _p(tile_entry), _p(tile_q0), tile_entry.numel(),
-                                 num_heads, num_kv_heads, page_size, float(scale),
-                                 int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
-                                 stream_ptr()),
+    check(lib.ri_attention_plain_ex(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache),
+                                    dtype_code(cache.dtype), _p(block_table), block_table.stride(0),
+                                    _p(cu_q), _p(kv_len), _p(tile_entry), _p(tile_q0), tile_entry.numel(),
+                                    num_heads, num_kv_heads, page_size, float(scale),
+                                    int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
+                                    float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
+                                    1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()),
           "attention_plain")
 
 
-def attention_single_supports(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None) -> bool:
-    """Whether the single-token attention kernel takes this geometry (up to 16 query heads a kv head,
+def _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key) -> int:
+    """Checks the fp32-arithmetic attention kernels share; returns the cache's page size."""
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype not in (cache.dtype, torch.float32):
+        raise KernelError("attention: q and cache share a dtype, out has it or is fp32; q and out have unit column stride")
+    _contig(cache, "cache")
+    if maps < 1 or num_heads % (num_kv_heads * maps):
+        raise KernelError("attention: heads (with their maps) must be a multiple of kv heads times maps")
+    if value_in_key and (maps != 1 or vd > head_dim):
+        raise KernelError("attention: values inside the keys are the keys' first channels, one map a head")
+    if sink_values is not None and (sink_values.dtype != torch.float32 or sink_values.numel() != num_heads
+                                    or not sink_values.is_contiguous()):
+        raise KernelError("attention: sink_values is fp32 [heads]")
+    return paged_cache_page_size(cache, num_kv_heads, head_dim, vd, maps, value_in_key)
+
+
+def attention_single_supports(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: Optional[int] = None,
+                              maps: int = 1) -> bool:
+    """Whether the single-token attention kernel takes this geometry (up to 16 query heads a key head,
     values up to 128 wide)."""
-    return bool(L.attention_plain(head_dim, value_dim or head_dim).ri_attention_single_supports(num_heads, num_kv_heads))
+    return bool(L.attention_plain(head_dim, value_dim or head_dim).ri_attention_single_supports(num_heads, num_kv_heads * maps))
 
 
 def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                      cu_q: torch.Tensor, kv_len: torch.Tensor, entry_list: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                      block: Optional[int] = None, value_dim: Optional[int] = None, sink: bool = False,
-                     splits: int = 1, part: Optional[torch.Tensor] = None) -> None:
+                     splits: int = 1, part: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
+                     sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
     """Attention of the entries that bring one token (`entry_list`, int32; -1 skips): fp32 arithmetic, a kv
     head's keys and values read once for all its query heads.  Arguments as `attention_plain`.  `splits` > 1
     cuts every entry's keys into that many ranges, a CTA each, joined by a second launch through `part`
     (fp32, `attention_single_scratch_floats` long)."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list, part)
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list, part, sink_values)
     if splits > 1 and (part is None or part.dtype != torch.float32 or not part.is_contiguous() or
                        part.numel() < attention_single_scratch_floats(entry_list.numel(), num_heads, value_dim or head_dim, splits)):
         raise KernelError("attention_single: the scratch for the key ranges is too small")
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"), (entry_list, "entry_list")):
         _i32(t, n)
-    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
-        raise KernelError("attention: q, out and cache share a dtype; q and out have unit column stride")
-    _contig(cache, "cache")
     vd = value_dim or head_dim
-    page_size = paged_cache_page_size(cache, num_kv_heads, head_dim, vd)
+    page_size = _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key)
     lib = L.attention_plain(head_dim, vd)
-    check(lib.ri_attention_single(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), dtype_code(cache.dtype),
-                                  _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list),
-                                  entry_list.numel(), num_heads, num_kv_heads, page_size, float(scale),
-                                  int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
-                                  int(splits), _p(part) if splits > 1 else None, stream_ptr()),
+    check(lib.ri_attention_single_ex(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), dtype_code(cache.dtype),
+                                     _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list),
+                                     entry_list.numel(), num_heads, num_kv_heads, page_size, float(scale),
+                                     int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
+                                     int(splits), _p(part) if splits > 1 else None,
+                                     float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
+                                     1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()),
           "attention_single", 2 if splits > 1 else 1)
 
 
@@ -460,16 +479,19 @@ def attention_single_scratch_floats(entries: int, num_heads: int, value_dim: int
     return entries * num_heads * splits * (value_dim + 2)
 
 
-def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int, value_dim: int) -> int:
+def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int, value_dim: int, maps: int = 1,
+                          value_in_key: bool = False) -> int:
     """Tokens a page of `cache` holds: [pages, 2, Hkv, page, hd] when keys and values have one size,
-    [pages, Hkv * page * (hd + vd)] (a page's keys, then its values) when they differ."""
+    [pages, page * (Hkv*maps*hd + Hkv*vd)] (a page's keys, then its values) when they differ or a value
+    head serves several key heads, [pages, page * Hkv*hd] when the values lie inside the keys."""
     if cache.dim() == 5:
-        if value_dim != head_dim or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        if (value_dim != head_dim or maps != 1 or value_in_key or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads
+                or cache.shape[4] != head_dim):
             raise KernelError("attention: cache must be [pages, 2, Hkv, page, head_dim]")
         return cache.shape[3]
-    per_token = num_kv_heads * (head_dim + value_dim)
+    per_token = num_kv_heads * maps * head_dim + (0 if value_in_key else num_kv_heads * value_dim)
     if cache.dim() != 2 or cache.shape[1] % per_token:
-        raise KernelError("attention: cache must be [pages, Hkv * page * (head_dim + value_dim)]")
+        raise KernelError("attention: cache must be [pages, page * (key heads * head_dim + value heads * value_dim)]")
     return cache.shape[1] // per_token
 
 
@@ -608,15 +630,21 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optio
                 k_weight: Optional[torch.Tensor], norm_mode: int, eps: float, positions: torch.Tensor,
                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
                 slot_of_token: Optional[torch.Tensor], cache: Optional[torch.Tensor], q_out: torch.Tensor,
-                num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, has_kv: bool) -> None:
+                num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, has_kv: bool,
+                value_heads: Optional[int] = None) -> None:
     """qkv [T, Hq*hd (+ Hkv*hd + Hkv*vd when `has_kv`)]: add `bias` (fp32), norm q and k (`norm_mode` 0: not;
     1: every head by its own root mean square, weights [hd]; 2: all heads at once, weights [Hq*hd] and
     [Hkv*hd]), rotate the first `rotary_dim` channels of every head (pairs (2i, 2i+1) when `interleaved`, else
-    (i, i + rotary_dim/2)), write q into q_out [T, Hq*hd] and k, v into the cache at slot_of_token[t]."""
+    (i, i + rotary_dim/2)), write q into q_out [T, Hq*hd] and k, v into the cache at slot_of_token[t].
+    `value_heads`: heads of v where they are fewer than the heads of k (`num_kv_heads` then counts the key
+    heads: kv heads times the attention maps of a head).  qkv may be the leading columns of wider rows."""
     require_cuda(qkv, bias, q_weight, k_weight, positions, cos, sin, slot_of_token, cache, q_out)
     _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
     T = qkv.shape[0]
-    cols = num_heads * head_dim + (num_kv_heads * (head_dim + value_dim) if has_kv else 0)
+    Hv = value_heads or num_kv_heads
+    if num_kv_heads % Hv:
+        raise KernelError("qkv_prepare: key heads are a multiple of value heads")
+    cols = num_heads * head_dim + (num_kv_heads * head_dim + Hv * value_dim if has_kv else 0)
     if qkv.stride(1) != 1 or qkv.shape[1] != cols:
         raise KernelError(f"qkv_prepare: qkv must be [T, {cols}] with unit column stride")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != cols or not bias.is_contiguous()):
@@ -639,12 +667,12 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optio
         _contig(cache, "cache")
         if cache.dtype != q_out.dtype:
             raise KernelError("qkv_prepare: the cache has q_out's dtype")
-        page = paged_cache_page_size(cache, num_kv_heads, head_dim, value_dim)
+        page = paged_cache_page_size(cache, Hv, head_dim, value_dim, num_kv_heads // Hv)
     check(L.core().ri_qkv_prepare(_p(qkv), dtype_code(qkv.dtype), qkv.stride(0), _p(bias), _p(q_weight), _p(k_weight),
                                   dtype_code(ws[0].dtype) if ws else 0, int(norm_mode), float(eps), _p(positions),
                                   _p(cos), _p(sin), int(rotary_dim), 1 if interleaved else 0, _p(slot_of_token), _p(cache),
                                   _p(q_out), dtype_code(q_out.dtype), T, num_heads, num_kv_heads, head_dim, value_dim,
-                                  1 if has_kv else 0, page, stream_ptr()), "qkv_prepare")
+                                  1 if has_kv else 0, page, Hv, stream_ptr()), "qkv_prepare")
 
 
 # ------------------------------------------------------------------------ routed experts
@@ -778,7 +806,7 @@ def gated_head_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, w
                                       dtype_code(out.dtype), T, num_heads, value_dim, stream_ptr()), "gated_head_norm")
 
 
-ACT_GELU_ERF, ACT_TANH, ACT_GELU_TANH = 0, 1, 2
+ACT_GELU_ERF, ACT_TANH, ACT_GELU_TANH, ACT_RELU_SQUARED, ACT_SILU = 0, 1, 2, 3, 4
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: int) -> None:
@@ -787,6 +815,15 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: int) -> None:
     if x.shape != out.shape or x.dtype != out.dtype:
         raise KernelError("activation: out has x's shape and dtype")
     check(L.core().ri_activation(_p(x), _p(out), dtype_code(x.dtype), x.numel(), int(kind), stream_ptr()), "activation")
+
+
+def activation_cols(x: torch.Tensor, kind: int) -> None:
+    """x [rows, cols] with unit column stride (the leading columns of wider rows, say), in place."""
+    require_cuda(x)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("activation_cols: x is [rows, cols] with unit column stride")
+    check(L.core().ri_activation_cols(_p(x), dtype_code(x.dtype), x.stride(0), x.shape[0], x.shape[1], int(kind),
+                                      stream_ptr()), "activation_cols")
 
 
 def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> None:
@@ -856,6 +893,26 @@ def gated_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tenso
                                         stream_ptr()), "gated_scan")
 
 
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, q_scale: float,
+               out: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, entries: int,
+               num_heads: int, key_dim: int, value_dim: int) -> None:
+    """Linear attention with decays that do not depend on the token, over every entry's tokens in order, from
+    and into state[slot]: S = diag(decay) S + k v^T, out = S^T (q * q_scale).  `decay` fp32 [H*dk] (a head's
+    one decay repeated over its key channels, or one per channel); the rest as `gated_scan`.  The walk is
+    `gated_scan`'s: every token reads the same row of decays."""
+    require_cuda(q, k, v, decay, out, state, cu_q, state_slots)
+    T, H, dk, dv = q.shape[0], num_heads, key_dim, value_dim
+    _scan_common(state, out, cu_q, state_slots, T, H, dk, dv, "decay_scan")
+    _cols(q, T, H * dk, q.dtype, "decay_scan: q"); _cols(k, T, H * dk, q.dtype, "decay_scan: k")
+    _cols(v, T, H * dv, q.dtype, "decay_scan: v")
+    if decay.dtype != torch.float32 or decay.numel() != H * dk or not decay.is_contiguous():
+        raise KernelError("decay_scan: decay is fp32 [H*dk]")
+    check(L.recurrent(dk).ri_gated_scan(_p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0), _p(decay), 0,
+                                        dtype_code(q.dtype), float(q_scale), _p(out), _p(state), _p(cu_q),
+                                        _p(state_slots), int(entries), H, dv, 1 if T == int(entries) else 0,
+                                        stream_ptr()), "decay_scan")
+
+
 def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tensor, za_bias: Optional[torch.Tensor],
                zw: torch.Tensor, zw_bias: Optional[torch.Tensor], decay_rate: float, unit_eps: float,
                out: torch.Tensor, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, entries: int,
@@ -884,6 +941,121 @@ def delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, za: torch.Tens
                                         _p(unit[1]), H * dk, dtype_code(r.dtype), _p(out), _p(state), _p(cu_q),
                                         _p(state_slots), int(entries), H, dv, 1 if T == int(entries) else 0,
                                         stream_ptr()), "delta_scan")
+
+
+# ------------------------------------------------- blocks that norm after the sum, and their mixers
+def embed_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[t,:] (fp32) = scale * table[ids[t],:]."""
+    require_cuda(ids, table, out)
+    _i32(ids, "ids"); _contig(table, "table"); _contig(out, "out")
+    if out.dtype != torch.float32 or out.shape != (ids.numel(), table.shape[1]):
+        raise KernelError(f"embed_scaled: out must be fp32 [{ids.numel()}, {table.shape[1]}]")
+    check(L.core().ri_embed_scaled(_p(ids), _p(table), dtype_code(table.dtype), float(scale), _p(out), ids.numel(),
+                                   table.shape[1], table.shape[0], stream_ptr()), "embed_scaled")
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (fp32) rounded to out's dtype."""
+    require_cuda(x, out)
+    _contig(x, "x"); _contig(out, "out")
+    if x.dtype != torch.float32 or x.shape != out.shape:
+        raise KernelError("round_rows: x is fp32 and out has its shape")
+    check(L.core().ri_round_rows(_p(x), _p(out), dtype_code(out.dtype), x.numel(), stream_ptr()), "round_rows")
+
+
+def scale_add_norm(h: torch.Tensor, delta: Optional[torch.Tensor], bias: Optional[torch.Tensor], alpha: float,
+                   weight: torch.Tensor, eps: float, act: Optional[torch.Tensor]) -> None:
+    """h (fp32 [T,d]) <- weight * rms(alpha * h + delta + bias), in place; `act` (may be None) gets the new
+    h rounded to its dtype.  delta fp32 or bf16; bias (may be None) has the weight's dtype."""
+    require_cuda(h, delta, bias, weight, act)
+    _contig(h, "h"); _contig(weight, "weight")
+    T, d = h.shape
+    if h.dtype != torch.float32 or weight.numel() != d:
+        raise KernelError("scale_add_norm: the stream is fp32 and the weight has a row's size")
+    if delta is not None and (delta.shape != h.shape or not delta.is_contiguous()):
+        raise KernelError("scale_add_norm: delta has the stream's shape")
+    if bias is not None and (bias.numel() != d or bias.dtype != weight.dtype or not bias.is_contiguous()):
+        raise KernelError("scale_add_norm: bias has a row's size and the weight's dtype")
+    if act is not None and (act.shape != h.shape or not act.is_contiguous()):
+        raise KernelError("scale_add_norm: act has the stream's shape")
+    check(L.core().ri_scale_add_norm(_p(h), _p(delta), dtype_code(delta.dtype) if delta is not None else 0, _p(bias),
+                                     float(alpha), _p(weight), dtype_code(weight.dtype), float(eps), _p(act),
+                                     dtype_code(act.dtype) if act is not None else 0, T, d, stream_ptr()),
+          "scale_add_norm")
+
+
+def row_norm_gate(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  out: torch.Tensor) -> None:
+    """out = weight * o / rms(o) * sigmoid(gate), the root mean square over the whole row: o fp32 [T, n],
+    gate [T, n] (may be a column view; None: no gate), weight [n]."""
+    require_cuda(o, gate, weight, out)
+    _contig(o, "o"); _contig(out, "out"); _contig(weight, "weight")
+    if o.dtype != torch.float32 or o.dim() != 2 or out.shape != o.shape or weight.numel() != o.shape[1]:
+        raise KernelError("row_norm_gate: o is fp32 [T, n], out has its shape, weight a row's size")
+    if gate is not None and (gate.shape != o.shape or gate.stride(1) != 1):
+        raise KernelError("row_norm_gate: gate is [T, n] with unit column stride")
+    check(L.core().ri_row_norm_gate(_p(o), _p(gate), dtype_code(gate.dtype) if gate is not None else 0,
+                                    gate.stride(0) if gate is not None else 0, _p(weight), dtype_code(weight.dtype),
+                                    float(eps), _p(out), dtype_code(out.dtype), o.shape[0], o.shape[1], stream_ptr()),
+          "row_norm_gate")
+
+
+def diff_combine(a: torch.Tensor, lam: float, out_scale: float, eps: float, gate: Optional[torch.Tensor],
+                 out: torch.Tensor, num_heads: int, value_dim: int) -> None:
+    """a fp32 [T, H*2*vd], a head's two attention maps side by side: out[t, h] = out_scale * o / rms(o) *
+    sigmoid(gate[t, h]) with o = a1 - lam * a2 and the root mean square over the head's vd values."""
+    require_cuda(a, gate, out)
+    _contig(a, "a"); _contig(out, "out")
+    T = a.shape[0]
+    if a.dtype != torch.float32 or a.shape != (T, num_heads * 2 * value_dim) or out.shape != (T, num_heads * value_dim):
+        raise KernelError("diff_combine: a is fp32 [T, H*2*vd], out [T, H*vd]")
+    if gate is not None and (gate.shape != out.shape or gate.stride(1) != 1):
+        raise KernelError("diff_combine: gate is [T, H*vd] with unit column stride")
+    check(L.core().ri_diff_combine(_p(a), float(lam), float(out_scale), float(eps), _p(gate),
+                                   dtype_code(gate.dtype) if gate is not None else 0,
+                                   gate.stride(0) if gate is not None else 0, _p(out), dtype_code(out.dtype), T,
+                                   num_heads, value_dim, stream_ptr()), "diff_combine")
+
+
+def latent_prepare(proj: torch.Tensor, c_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                   cos: torch.Tensor, sin: torch.Tensor, slot_of_token: Optional[torch.Tensor],
+                   cache: Optional[torch.Tensor], q_plain: torch.Tensor, q_full: torch.Tensor, num_heads: int,
+                   head_dim: int, rot_dim: int, rank: int) -> None:
+    """proj [T, H*(d+r) + rank + r]: every head's plain (d) and rotated (r) query channels, then the low-rank
+    vector and the key part all heads share.  Writes the plain query parts into q_plain [T, H*d], the rotated
+    ones into the last r channels of every head of q_full [T, H*(rank+r)], and the cache row of the token
+    (the low-rank vector normed with c_weight, then the rotated shared key part) at slot_of_token[t]."""
+    require_cuda(proj, c_weight, positions, cos, sin, slot_of_token, cache, q_plain, q_full)
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
+    T, H, d, r = proj.shape[0], num_heads, head_dim, rot_dim
+    if proj.stride(1) != 1 or proj.shape[1] != H * (d + r) + rank + r:
+        raise KernelError(f"latent_prepare: proj is [T, {H * (d + r) + rank + r}] with unit column stride")
+    _contig(q_plain, "q_plain"); _contig(q_full, "q_full"); _contig(c_weight, "c_weight")
+    if q_plain.shape != (T, H * d) or q_full.shape != (T, H * (rank + r)) or q_plain.dtype != q_full.dtype:
+        raise KernelError("latent_prepare: q_plain is [T, H*d], q_full [T, H*(rank+r)], of one dtype")
+    if c_weight.numel() != rank:
+        raise KernelError("latent_prepare: the norm weight has the low-rank vector's size")
+    for t in (cos, sin):
+        if t.dtype != torch.float32 or t.shape[1] != r // 2 or not t.is_contiguous():
+            raise KernelError("latent_prepare: cos/sin are fp32 [positions, r/2]")
+    if cache is not None:
+        _contig(cache, "cache")
+        if cache.dtype != q_full.dtype or cache.dim() != 2 or cache.shape[1] % (rank + r):
+            raise KernelError("latent_prepare: the cache is [pages, page*(rank+r)] of q's dtype")
+    check(L.core().ri_latent_prepare(_p(proj), dtype_code(proj.dtype), proj.stride(0), _p(c_weight),
+                                     dtype_code(c_weight.dtype), float(eps), _p(positions), _p(cos), _p(sin),
+                                     _p(slot_of_token), _p(cache), _p(q_plain), _p(q_full), dtype_code(q_full.dtype),
+                                     T, H, d, r, rank, stream_ptr()), "latent_prepare")
+
+
+def bias_rows(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x [T, n] += bias [n], in place."""
+    require_cuda(x, bias)
+    _contig(x, "x"); _contig(bias, "bias")
+    if x.dim() != 2 or bias.numel() != x.shape[1]:
+        raise KernelError("bias_rows: bias has a row's size")
+    check(L.core().ri_bias_rows(_p(x), dtype_code(x.dtype), _p(bias), dtype_code(bias.dtype), x.shape[0], x.shape[1],
+                                stream_ptr()), "bias_rows")
 
 
 def _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim):

@@ -42,7 +42,17 @@ _SIGNATURES = {
     "ri_attention_single": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _P],
     "ri_embed_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_hyper_collect": [_P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _P],
-    "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_attention_plain_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _I, _P],
+    "ri_attention_single_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _F, _P, _I, _I, _I, _P],
+    "ri_embed_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
+    "ri_round_rows": [_P, _P, _I, _L, _P],
+    "ri_scale_add_norm": [_P, _P, _I, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
+    "ri_row_norm_gate": [_P, _P, _I, _I, _P, _I, _F, _P, _I, _I, _I, _P],
+    "ri_diff_combine": [_P, _F, _F, _F, _P, _I, _I, _P, _I, _I, _I, _I, _P],
+    "ri_latent_prepare": [_P, _I, _I, _P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ri_bias_rows": [_P, _I, _P, _I, _I, _I, _P],
+    "ri_activation_cols": [_P, _I, _I, _I, _I, _I, _P],
     "ri_moe_route": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ri_moe_sort": [_P, _P, _I, _I, _P, _P, _P, _P],
     "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -63,7 +73,7 @@ _SIGNATURES = {
 }
 
 _CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu", "sequence_parts.cu", "stream_parts.cu",
-                 "mixture_parts.cu"]
+                 "mixture_parts.cu", "postnorm_parts.cu"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 
 

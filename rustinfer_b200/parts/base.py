@@ -45,16 +45,31 @@ class PagedKV:
     """Keys and values of every token (or of the last `window` tokens, or of the tokens of the
     current block of `block` positions) in pages.  `value_dim`: size of a value where it is not
     the keys' `head_dim`; a page then holds its keys [kv head][slot][head_dim] followed by its
-    values [kv head][slot][value_dim]."""
+    values [kv head][slot][value_dim].  `key_maps` m > 1: every kv head has m key heads (the attention
+    maps of a head, each with keys of its own) over one head of values; a page holds
+    [kv head][map][slot][head_dim], then the values.  `value_in_key`: a key's value is its own first
+    `value_dim` channels, and a page holds keys only."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
     block: Optional[int] = None
+    key_maps: int = 1
+    value_in_key: bool = False
 
     @property
     def v_dim(self) -> int:
         return self.value_dim or self.head_dim
+
+    @property
+    def plain(self) -> bool:
+        """Keys and values of one size, a key head a value head: stored [page][K|V][kv head][slot][head_dim]."""
+        return self.v_dim == self.head_dim and self.key_maps == 1 and not self.value_in_key
+
+    def elems_per_token(self) -> int:
+        """Elements of one layer's cache a token takes."""
+        keys = self.num_kv_heads * self.key_maps * self.head_dim
+        return keys if self.value_in_key else keys + self.num_kv_heads * self.v_dim
 
     def first_key_kept(self, length: int) -> int:
         """The first position the token at position `length` (the next one) can still see."""

@@ -23,6 +23,7 @@ class Hidden:
     stream: torch.Tensor                # [T, hidden] fp32 ([streams, T, hidden] in a model of several streams)
     pending: Optional[torch.Tensor]     # [T, hidden] activation dtype, not yet added
     fresh: bool = False                 # several streams of which only the first is written yet (all are equal)
+    act: Optional[torch.Tensor] = None  # the stream rounded to the activation dtype, where a block keeps one
 
 
 class Block:
@@ -114,7 +115,35 @@ def _hyper(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
         hidden.pending = HyperPending(block.ffn.forward(x, step), block.ffn_norm)
 
 
-ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich, "hyper": _hyper}
+def _post_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    """The norm after the sum, and the stream replaced by it:
+
+        h <- mixer_norm(alpha h + mixer(h));  h <- ffn_norm(alpha h + ffn(h))
+
+    (the second line only when the layer has a feed-forward).  The sublayers read the stream itself;
+    both norms are `post_rmsnorm` parts, which hold alpha.  The stream is fp32; each norm also hands
+    out its result rounded to the activation dtype, which is what the next sublayer's products read
+    (`hidden.act`; the first block of a model rounds the stem's output itself)."""
+    from ..ops import kernels as K
+    from .norm import PostRMSNorm
+    if not isinstance(block.mixer_norm, PostRMSNorm) or (block.ffn is not None and not isinstance(block.ffn_norm, PostRMSNorm)):
+        raise ValueError("the post_norm arrangement wants a post_rmsnorm after each sublayer")
+    if hidden.pending is not None:
+        raise ValueError("the post_norm arrangement follows blocks that leave nothing pending")
+    x = hidden.act
+    if x is None:
+        x = hidden.stream
+        if block.mixer_norm.ctx.dtype != torch.float32:
+            x = torch.empty(hidden.stream.shape, dtype=block.mixer_norm.ctx.dtype, device=hidden.stream.device)
+            K.round_rows(hidden.stream, x)
+    x = block.mixer_norm.renorm(hidden.stream, block.mixer.forward(x, step, cache))
+    if block.ffn is not None:
+        x = block.ffn_norm.renorm(hidden.stream, block.ffn.forward(x, step))
+    hidden.act = x
+
+
+ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich, "hyper": _hyper,
+                                     "post_norm": _post_norm}
 
 
 def register_arrangement(name: str, fn: Callable) -> None:

@@ -59,13 +59,14 @@ class SwiGLU(FeedForward):
         return self.down(m, out_dtype=torch.float32 if self.out_fp32 else self.ctx.dtype)
 
 
-_ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.ACT_TANH, "gelu_tanh": K.ACT_GELU_TANH}
+_ACTIVATIONS = {"gelu": K.ACT_GELU_ERF, "gelu_erf": K.ACT_GELU_ERF, "tanh": K.ACT_TANH, "gelu_tanh": K.ACT_GELU_TANH,
+                "relu_squared": K.ACT_RELU_SQUARED, "silu": K.ACT_SILU}
 
 
 @register_feed_forward("dense_mlp")
 class DenseMLP(FeedForward):
     """down( act(up(x)) ) without a gate.  params: hidden_size, intermediate_size, activation
-    ("gelu": with erf; "gelu_tanh"; "tanh"), up_name / down_name (tensor names, default
+    ("gelu": with erf; "gelu_tanh"; "tanh"; "relu_squared": max(z, 0)^2; "silu"), up_name / down_name (tensor names, default
     "up_proj.weight" / "down_proj.weight"), output ("float32": the result leaves the down projection in
     32-bit).  The activation is computed in fp32."""
 

@@ -176,3 +176,71 @@ class DeltaRule(_StateMixer):
         y = torch.empty((T, self.H * self.dk), dtype=dt, device=x.device)
         K.gated_head_norm(o, p["g"], self.norm_w, True, K.GATE_SIGMOID, self.norm_eps, y, self.H, self.dk)
         return self.o(y, out_dtype=dt)
+
+
+@register_mixer("lightning_attention")
+class LightningAttention(Mixer):
+    """Linear attention with one fixed decay per head:
+
+        q = silu(W_q h), k = silu(W_k h), v = silu(W_v h);  S_t = decay_h S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t
+        out = W_o( w * rms(o over all heads) * sigmoid(W_g h) )
+
+    params: hidden_size, num_heads, key_dim, value_dim, decay (one number per head), norm_eps, q_scale
+    (default 1), tensor_names.  Tensors: q, k [H*dk, hidden]; v, g [H*dv, hidden]; norm [H*dv]; o [hidden,
+    H*dv].  The four projections are one product whose result stays fp32: the activations are formed from
+    it in fp32 and the recurrence reads them unrounded, so the decays, the state and everything that
+    enters it are 32-bit in both engine precisions.  The walk is the gated recurrence's with the same row
+    of decays for every token."""
+    graph_safe = True
+    joined = ["q", "k", "v", "g"]
+
+    def __init__(self, params):
+        super().__init__(params)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.H, self.dk = int(p["num_heads"]), int(p["key_dim"])
+        self.dv = int(p.get("value_dim") or self.dk)
+        self.decay = [float(x) for x in p["decay"]]
+        self.norm_eps = float(p["norm_eps"])
+        self.q_scale = float(p.get("q_scale", 1.0))
+        self.tensor_names = dict(p.get("tensor_names") or {})
+        if len(self.decay) != self.H:
+            raise ValueError(f"{len(self.decay)} decays for {self.H} heads")
+        if not (1 <= self.dk <= 512 and self.dv >= 1):
+            raise ValueError(f"key size {self.dk}: the recurrence kernels take key sizes up to 512")
+
+    def _name(self, local: str) -> str:
+        return self.tensor_names.get(local, local)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        n, qk, vg = self._name, self.H * self.dk, self.H * self.dv
+        return {n("q"): ParamDecl((qk, self.hidden)), n("k"): ParamDecl((qk, self.hidden)),
+                n("v"): ParamDecl((vg, self.hidden)), n("g"): ParamDecl((vg, self.hidden)),
+                n("norm"): ParamDecl((vg,), init="ones"), n("o"): ParamDecl((self.hidden, vg))}
+
+    def cache_need(self):
+        return FixedState((self.H, self.dv, K.recurrent_state_rows(self.dk)), "float32")
+
+    def prepare(self, ctx) -> None:
+        super().prepare(ctx)
+        per_channel = [d for d in self.decay for _ in range(self.dk)]
+        self.decay_row = torch.tensor(per_channel, dtype=torch.float64).to(torch.float32).to(ctx.device)
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self._name
+        parts = [tensors[n(x)] for x in self.joined]
+        dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
+        self.proj = Linear(torch.cat([t.to(dt) for t in parts], dim=0), self.ctx.num_sms)
+        self.norm_w = tensors[n("norm")].contiguous()
+        self.o = Linear(tensors[n("o")], self.ctx.num_sms)
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: StateLayerCache) -> torch.Tensor:
+        T, qk, vg = x.shape[0], self.H * self.dk, self.H * self.dv
+        p = self.proj(x, out_dtype=torch.float32)
+        K.activation_cols(p[:, : 2 * qk + vg], K.ACT_SILU)
+        o = torch.empty((T, vg), dtype=torch.float32, device=x.device)
+        K.decay_scan(p[:, :qk], p[:, qk: 2 * qk], p[:, 2 * qk: 2 * qk + vg], self.decay_row, self.q_scale, o,
+                     cache.state, step.cu_q, step.state_slots, step.num_entries, self.H, self.dk, self.dv)
+        y = torch.empty((T, vg), dtype=self.ctx.dtype, device=x.device)
+        K.row_norm_gate(o, p[:, 2 * qk + vg:], self.norm_w, self.norm_eps, y)
+        return self.o(y, out_dtype=torch.float32)

@@ -37,6 +37,43 @@ class RMSNorm(Norm):
         return out
 
 
+@register_norm("post_rmsnorm")
+class PostRMSNorm(Norm):
+    """The norm of a block that norms after the sum: h <- w * rms(alpha * h + y), the stream itself
+    replaced.  params: size, eps, alpha (default 1), weight_name (default "weight").  `renorm` does
+    that in one kernel and returns the new stream in the activation dtype for the next sublayer's
+    products (the stream itself in a 32-bit engine); `add_norm` is the plain RMS norm, so the part
+    can stand wherever an `rmsnorm` can."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.alpha = float(params.get("alpha", 1.0))
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.weight_name: ParamDecl((self.size,), init="ones")}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def renorm(self, h: torch.Tensor, delta: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.ctx.dtype == torch.float32:
+            K.scale_add_norm(h, delta, bias, self.alpha, self.weight, self.eps, None)
+            return h
+        act = torch.empty(h.shape, dtype=self.ctx.dtype, device=h.device)
+        K.scale_add_norm(h, delta, bias, self.alpha, self.weight, self.eps, act)
+        return act
+
+    def add_norm(self, h, delta, rows=None):
+        n = h.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=h.device)
+        K.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
+        return out
+
+
 @dataclass
 class NormedDelta:
     """A sublayer's output that is to pass through `norm` before it is added to the stream (a

@@ -41,6 +41,27 @@ class TokenEmbedding(Embedding):
         K.embed_gather(step.token_ids[: step.num_tokens], self.table, h)
 
 
+@register_embedding("scaled_embedding")
+class ScaledEmbedding(TokenEmbedding):
+    """h[t, :] = scale * E[ids[t], :], the product in fp32.  The table itself is not scaled, so a head that
+    shares it multiplies by the stored rows.  params: vocab_size, hidden_size, scale, weight_name (default
+    "weight")."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.scale = float(params.get("scale", 1.0))
+        self.weight_name = str(params.get("weight_name", "weight"))
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.weight_name: ParamDecl((self.vocab, self.hidden))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.table = tensors[self.weight_name].contiguous()
+
+    def forward(self, step: StepContext, h: torch.Tensor) -> None:
+        K.embed_scaled(step.token_ids[: step.num_tokens], self.table, self.scale, h)
+
+
 @register_embedding("sinusoid_embedding")
 class SinusoidEmbedding(TokenEmbedding):
     """h[t, :] = E[ids[t], :] + s(p_t), with s(p)[2i] = sin(p * base^(-2i/hidden)) and s(p)[2i+1] the
