@@ -206,8 +206,11 @@ class SotazenConfig:
 
     def to_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = {"architecture": self.architecture, "width": self.width, "vocab": self.vocab,
-                             "norm": {"eps": self.norm_eps}, "embedding": {"scale": self.embedding_scale},
-                             "postln_alpha": self.postln_alpha, "layers": [l.to_dict() for l in self.layers]}
+                             "norm": {"eps": self.norm_eps}, "layers": [l.to_dict() for l in self.layers]}
+        if self.embedding_scale != 1.0:
+            d["embedding"] = {"scale": self.embedding_scale}
+        if self.postln_alpha != 1.0:
+            d["postln_alpha"] = self.postln_alpha
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids)
         return d

@@ -63,6 +63,35 @@ def softmax_rows(scores: torch.Tensor, mask: torch.Tensor, sink: Optional[torch.
     return e / den
 
 
+def two_map_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, softcap: Optional[float],
+                      window: Optional[int]) -> torch.Tensor:
+    """q [T, H, 2, d], k [T, G, 2, d], v [T, G, vd] (already normed and rotated): for every head and map an
+    ordinary softmax attention of its own over the values of the head's kv head; [T, H, 2, vd]."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    rep = H // G
+    mask = visible(T, window)
+    vh = v.permute(1, 0, 2).repeat_interleave(rep, dim=0)                  # [H, T, vd]
+    out = []
+    for j in range(2):
+        qj = q[:, :, j].permute(1, 0, 2)                                   # [H, T, d]
+        kj = k[:, :, j].permute(1, 0, 2).repeat_interleave(rep, dim=0)     # [H, T, d]
+        s = (qj @ kj.transpose(1, 2)) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        out.append(softmax_rows(s, mask) @ vh)
+    return torch.stack(out, dim=2).permute(1, 0, 2, 3)                     # [T, H, 2, vd]
+
+
+def map_weight(w: Mapping[str, torch.Tensor], diff: float) -> float:
+    """lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff."""
+    return math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + diff
+
+
+def difference_of_maps(maps: torch.Tensor, lam: float, diff: float, eps: float) -> torch.Tensor:
+    """maps [T, H, 2, vd] -> (1 - diff) * rms_head(a1 - lam a2), [T, H, vd]."""
+    return rms_norm(maps[:, :, 0] - lam * maps[:, :, 1], None, eps) * (1.0 - diff)
+
+
 def differential_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float) -> torch.Tensor:
     """Two softmax maps per head over the same values, the second subtracted with a learned weight."""
     T = h.shape[0]
@@ -82,45 +111,52 @@ def differential_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Ma
     if rot:
         q = rotate_pairs(q, pos, rot["dims"], rot["base"])
         k = rotate_pairs(k, pos, rot["dims"], rot["base"])
-    rep = H // G
-    mask = visible(T, (m.get("mask") or {}).get("size"))
+    maps = two_map_attention(q, k, v, m["scale"], m.get("softcap"), (m.get("mask") or {}).get("size"))
     diff = float(m["diff"])
-    lam = (math.exp(float((w["lq1"] * w["lk1"]).sum())) - math.exp(float((w["lq2"] * w["lk2"]).sum())) + diff)
-    maps = []
-    for j in range(2):
-        qj = q[:, :, j].permute(1, 0, 2)                                  # [H, T, d]
-        kj = k[:, :, j].permute(1, 0, 2).repeat_interleave(rep, dim=0)    # [H, T, d]
-        s = (qj @ kj.transpose(1, 2)) * m["scale"]
-        cap = m.get("softcap")
-        if cap:
-            s = cap * torch.tanh(s / cap)
-        p = softmax_rows(s, mask)
-        maps.append(p @ v.permute(1, 0, 2).repeat_interleave(rep, dim=0))  # [H, T, vd]
-    o = maps[0] - lam * maps[1]
-    o = rms_norm(o, None, eps) * (1.0 - diff)
-    o = o.permute(1, 0, 2).reshape(T, H * vd)
+    o = difference_of_maps(maps, map_weight(w, diff), diff, eps).reshape(T, H * vd)
     if "g" in w:
         o = o * torch.sigmoid(h @ w["g"].T)
     y = o @ w["o"].T
     return y + w["o.b"] if "o.b" in w else y
 
 
+def decay_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor,
+                     state: Optional[torch.Tensor] = None):
+    """q, k [T, H, d], v [T, H, vd], decay [H]: S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t, token by
+    token from `state` [H, d, vd] (zero if None).  Returns (o [T, H, vd], the last state)."""
+    T, H, d = q.shape
+    S = torch.zeros(H, d, v.shape[2], dtype=F64) if state is None else state.clone()
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return out, S
+
+
 def lightning_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float) -> torch.Tensor:
-    """S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per head, token by token from a zero state."""
+    """Linear attention with one fixed decay per head, silu on q, k and v, a norm over all heads and a gate."""
     T = h.shape[0]
     H, d, vd = m["heads"], m["dim"], m["vdim"]
     silu = torch.nn.functional.silu
     q = silu(h @ w["q"].T).reshape(T, H, d)
     k = silu(h @ w["k"].T).reshape(T, H, d)
     v = silu(h @ w["v"].T).reshape(T, H, vd)
-    decay = torch.tensor([float(x) for x in m["decay"]], dtype=F64)
-    S = torch.zeros(H, d, vd, dtype=F64)
-    out = torch.zeros(T, H, vd, dtype=F64)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    out, _ = decay_recurrence(q, k, v, torch.tensor([float(x) for x in m["decay"]], dtype=F64))
     o = rms_norm(out.reshape(T, H * vd), w["norm"], eps) * torch.sigmoid(h @ w["g"].T)
     return o @ w["o"].T
+
+
+def latent_scores_attention(q_plain: torch.Tensor, q_rot: torch.Tensor, c: torch.Tensor, k_rot: torch.Tensor,
+                            uk: torch.Tensor, uv: torch.Tensor, scale: float, sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """q_plain [T, H, d], q_rot [T, H, r] (rotated), c [T, rank] (normed), k_rot [T, r] (rotated), uk [H*d, rank],
+    uv [H*vd, rank]: keys and values of every head are made from c; causal softmax with exp(sink_h) in the
+    denominator; [T, H, vd]."""
+    T, H, d = q_plain.shape
+    k_plain = (c @ uk.T).reshape(T, H, d)
+    v = (c @ uv.T).reshape(T, H, -1)
+    s = torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihr,jr->hij", q_rot, k_rot)
+    p = softmax_rows(s * scale, visible(T, None), sink)
+    return torch.einsum("hij,jhv->ihv", p, v)
 
 
 def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping, eps: float) -> torch.Tensor:
@@ -129,18 +165,13 @@ def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping,
     T = h.shape[0]
     H, d, r, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = torch.arange(T)
-    base = m["rot"]["base"]
+    base = (m.get("rot") or {}).get("base", 10000.0)
     q = (h @ w["q"].T).reshape(T, H, d + r)
-    q_plain, q_rot = q[..., :d], rotate_pairs(q[..., d:], pos, r, base)
     dkv = h @ w["dkv"].T
     c = rms_norm(dkv[:, :rank], w["dkv.norm"], eps)
-    k_rot = rotate_pairs(dkv[:, rank:], pos, r, base)                     # [T, r]
-    k_plain = (c @ w["uk"].T).reshape(T, H, d)
-    v = (c @ w["uv"].T).reshape(T, H, vd)
-    s = torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihr,jr->hij", q_rot, k_rot)
-    p = softmax_rows(s * m["scale"], visible(T, None), w["sink"] if "sink" in w else None)
-    o = torch.einsum("hij,jhv->ihv", p, v).reshape(T, H * vd)
-    return o @ w["o"].T
+    o = latent_scores_attention(q[..., :d], rotate_pairs(q[..., d:], pos, r, base), c,
+                                rotate_pairs(dkv[:, rank:], pos, r, base), w["uk"], w["uv"], m["scale"], w.get("sink"))
+    return o.reshape(T, H * vd) @ w["o"].T
 
 
 def feed_forward(h: torch.Tensor, w: Mapping[str, torch.Tensor]) -> torch.Tensor:
@@ -154,6 +185,16 @@ MIXERS = {"attention": differential_attention, "lightning": lightning_attention,
 
 def _sub(weights: Mapping[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
     return {k[len(prefix):]: v.to(F64) for k, v in weights.items() if k.startswith(prefix)}
+
+
+def read_model_folder(folder: str):
+    """(config.json as a dict, tensors by name) of a model folder."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(folder, "model.safetensors"))
 
 
 def forward(cfg: Mapping, weights: Mapping[str, torch.Tensor], tokens: List[int], taps: Optional[list] = None) -> torch.Tensor:
