@@ -17,7 +17,7 @@ attention), the Llama-3.2-3B-shaped model at 8 of its 28 layers serving 64 reque
 this engine's attention and GEMM kernels timed against the reference's own attention kernels
 (compiled unmodified, see baseline/reference_kernels.py) and the library GEMM on the same data.
 `--shape` takes the layer sizes of the 3B or 8B benchmark configuration for the headline instead;
-`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` (or `pikalix`) leaves
+`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` (or `pikalix`, `sotazen`) leaves
 all of that aside and prints a line of its own: prefill and decode of that family's models at two sizes beside
 Llama models of the same width, depth, feed-forward width and vocabulary, and that family's kernels alone against
 their rooflines.
@@ -764,8 +764,213 @@ def pikalix_kernels(hbm_gbs, bf16_tflops, size):
     return out
 
 
+def _sotazen(width, layers, ff, vocab, lightning, latent, attn, window, rot):
+    """`layers` layers in the order lightning, lightning, latent attention, differential attention (norms after the
+    sums), a dense feed-forward with the square of relu in each."""
+    lh, ld, lv = lightning
+    th, td, tr, tv, rank = latent
+    ah, akv, ad, av = attn
+    out = []
+    for i in range(layers):
+        mlp = {"ff": ff, "kind": "dense"}
+        if i % 4 == 3:
+            mixer = {"heads": ah, "kv_heads": akv, "dim": ad, "vdim": av, "scale": ad ** -0.5, "diff": 0.8, "softcap": 50.0,
+                     "mask": {"size": window}, "rot": {"dims": rot, "base": 500000.0}}
+            out.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+        elif i % 4 == 2:
+            mixer = {"heads": th, "dim": td, "rot_dim": tr, "vdim": tv, "kv_rank": rank, "scale": (td + tr) ** -0.5,
+                     "rot": {"dims": tr, "base": 10000.0}}
+            out.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            decay = [1.0 - 2.0 ** (-5.0 - 3.0 * h / max(lh - 1, 1)) for h in range(lh)]
+            out.append({"type": "lightning", "mixer": {"heads": lh, "dim": ld, "vdim": lv, "decay": decay}, "mlp": mlp})
+    return {"architecture": "Sotazen", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "postln_alpha": 2.0, "layers": out}
+
+
+# Sotazen at the same widths: lightning (heads, key, value), latent attention (heads, plain, rotated, value, rank),
+# differential attention (heads, kv heads, key of one map, value), its window and rotated channels
+SOTAZEN_SIZES = {
+    "w1024": dict(width=1024, layers=8, ff=4096, vocab=32768, lightning=(8, 128, 128), latent=(16, 64, 32, 64, 128),
+                  attn=(8, 2, 64, 128), window=1024, rot=32, llama=(16, 4, 64)),
+    "w2048": dict(width=2048, layers=8, ff=8192, vocab=32768, lightning=(16, 128, 128), latent=(32, 64, 32, 64, 256),
+                  attn=(16, 4, 64, 128), window=1024, rot=32, llama=(32, 8, 64)),
+}
+
+
+def sotazen_kernels(hbm_gbs, bf16_tflops, size):
+    """The Sotazen kernels alone at one size, each beside the like kernel of the nearest existing family on the same
+    shapes (the gated recurrence and head norm of Dirurax, the window attention with a sink and the q/k/v preparation
+    of Pikalix, the add + RMSNorm and rotary kernels of the Llama path): microseconds, and what that is of the bytes
+    they must move at the measured copy bandwidth."""
+    import torch
+    from rustinfer_b200.ops import kernels as K
+    from rustinfer_b200.parts.attention_variants import PlainAttend
+    from rustinfer_b200.parts.base import BuildContext
+    dev = torch.device("cuda:0")
+    sz = SOTAZEN_SIZES[size]
+    d = sz["width"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)
+    f32 = lambda *s: torch.randn(*s, device=dev)
+    frac = lambda moved, us: round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    fma_per_s = sms * 128 * 1.9e9
+    out = {}
+    ah, akv, ad, av = sz["attn"]
+    th, td, tr, tv, rank = sz["latent"]
+    kd = rank + tr
+    for tag, T, entries in (("prefill2048", 2048, 1), ("decode64", 64, 64)):
+        cu = i32([i * (T // entries) for i in range(entries + 1)])
+        slots = i32(list(range(entries)))
+        # the norm after the sum beside the add + RMSNorm before a sublayer
+        h, delta, w = f32(T, d), f32(T, d), bf(d)
+        xo = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.scale_add_norm(h, delta, None, 2.0, w, 1e-6, xo), flush=flush)
+        d16 = bf(T, d)
+        us_rms = time_kernel(lambda: K.add_rmsnorm(h, d16, w, 1e-6, xo), flush=flush)
+        out[f"scale_add_norm_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * d * (4 + 4 + 4 + 2), us),
+                                        "add_rmsnorm_us": round(us_rms, 1), "add_rmsnorm_hbm_frac": frac(T * d * (4 + 4 + 2 + 2), us_rms)}
+        # lightning: the walk with fixed decays beside the gated walk on the same sizes, the row norm beside the head norm
+        H, dk, dv = sz["lightning"]
+        p32 = f32(T, 2 * H * dk + 2 * H * dv)
+        decay = torch.full((H * dk,), 0.97, device=dev)
+        o = torch.empty(T, H * dv, device=dev)
+        state = torch.zeros(entries + 1, H, dv, K.recurrent_state_rows(dk), device=dev)
+        us = time_kernel(lambda: K.decay_scan(p32[:, :H * dk], p32[:, H * dk:2 * H * dk], p32[:, 2 * H * dk:2 * H * dk + H * dv],
+                                              decay, 1.0, o, state, cu, slots, entries, H, dk, dv), flush=flush)
+        moved = T * (2 * H * dk * 4 + H * dv * 4 + H * dv * 4) + 2 * entries * H * dk * dv * 4
+        p16, z = bf(T, 2 * H * dk + 2 * H * dv), f32(T, H * dk)
+        zb = bf(H * dk)
+        us_g = time_kernel(lambda: K.gated_scan(p16[:, :H * dk], p16[:, H * dk:2 * H * dk], p16[:, 2 * H * dk:2 * H * dk + H * dv],
+                                                z, zb, 1.0, 16.0, o, state, cu, slots, entries, H, dk, dv), flush=flush)
+        moved_g = T * (2 * H * dk * 2 + H * dv * 2 + H * dk * 4 + H * dv * 4) + 2 * entries * H * dk * dv * 4
+        out[f"decay_scan_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(moved, us),
+                                    "fma_frac": round(2 * T * H * dk * dv / (us * 1e-6) / fma_per_s, 4),
+                                    "gated_scan_us": round(us_g, 1), "gated_scan_hbm_frac": frac(moved_g, us_g)}
+        y = torch.empty(T, H * dv, device=dev, dtype=torch.bfloat16)
+        wn = bf(H * dv)
+        us = time_kernel(lambda: K.row_norm_gate(o, p32[:, 2 * H * dk + H * dv:], wn, 1e-6, y), flush=flush)
+        whd = bf(dv)
+        us_h = time_kernel(lambda: K.gated_head_norm(o, p16[:, 2 * H * dk + H * dv:], whd, False, K.GATE_SILU, 1e-6, y, H, dv), flush=flush)
+        out[f"row_norm_gate_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * H * dv * (4 + 4 + 2), us),
+                                       "gated_head_norm_us": round(us_h, 1), "gated_head_norm_hbm_frac": frac(T * H * dv * (4 + 2 + 2), us_h)}
+        # differential attention: q, k, v from the projection (two maps), the maps' difference with its norm and gate
+        cols = (ah + akv) * 2 * ad + akv * av
+        pages = T // PAGE + 1
+        cache = bf(pages, PAGE * (akv * 2 * ad + akv * av))
+        qkv32, bias = f32(T, cols), f32(cols)
+        qw, kw = bf(ad), bf(ad)
+        pos, slot_t = i32(list(range(T))), i32(list(range(T)))
+        cos, sin = f32(T, sz["rot"] // 2), f32(T, sz["rot"] // 2)
+        q_out = torch.empty(T, ah * 2 * ad, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.qkv_prepare(qkv32, bias, qw, kw, 1, 1e-6, pos, cos, sin, sz["rot"], True, slot_t, cache, q_out,
+                                               2 * ah, 2 * akv, ad, av, True, value_heads=akv), flush=flush)
+        lh, lkv, lhd = sz["llama"]
+        lcols = (lh + 2 * lkv) * lhd
+        qkv16 = bf(T, lcols)
+        lcache = bf(pages, 2, lkv, PAGE, lhd)
+        cos2, sin2 = f32(T, lhd // 2), f32(T, lhd // 2)
+        us_rope = time_kernel(lambda: K.rope_scatter(qkv16, pos, cos2, sin2, slot_t, lcache, lh, lkv, lhd, lhd), flush=flush)
+        out[f"qkv_prepare_two_maps_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * cols * (4 + 2), us),
+                                              "rope_scatter_us": round(us_rope, 1), "rope_scatter_hbm_frac": frac(T * lcols * (2 + 2), us_rope)}
+        maps, gate = f32(T, ah * 2 * av), f32(T, ah * av)
+        yd = torch.empty(T, ah * av, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.diff_combine(maps, 0.7, 0.2, 1e-6, gate, yd, ah, av), flush=flush)
+        o2, g16, w2 = f32(T, ah * av), bf(T, ah * av), bf(av)
+        us_h = time_kernel(lambda: K.gated_head_norm(o2, g16, w2, False, K.GATE_SILU, 1e-6, yd, ah, av), flush=flush)
+        out[f"diff_combine_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * ah * av * (8 + 4 + 2), us),
+                                      "gated_head_norm_us": round(us_h, 1), "gated_head_norm_hbm_frac": frac(T * ah * av * (4 + 2 + 2), us_h)}
+        # latent attention: queries and the cached row from the projection
+        pcols = th * (td + tr) + kd
+        proj, cw = f32(T, pcols), bf(rank)
+        lat_cache = bf(pages, PAGE * kd)
+        cos3, sin3 = f32(T, tr // 2), f32(T, tr // 2)
+        q_plain = torch.empty(T, th * td, device=dev, dtype=torch.bfloat16)
+        q_full = torch.empty(T, th * kd, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.latent_prepare(proj, cw, 1e-6, pos, cos3, sin3, slot_t, lat_cache, q_plain, q_full, th, td, tr, rank),
+                         flush=flush)
+        out[f"latent_prepare_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * (pcols * 4 + (th * (td + tr) + kd) * 2), us),
+                                        "rope_scatter_us": round(us_rope, 1), "rope_scatter_hbm_frac": frac(T * lcols * (2 + 2), us_rope)}
+    # attention of 64 single tokens at 4,096 keys: two maps under the window, rows of the latent cache, and Pikalix's
+    # window attention with a sink on the Llama heads
+    B, ctx, win = 64, 4096, sz["window"]
+    blocks = ctx // PAGE
+    bctx = BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=B, num_sms=sms)
+    kv_len, cu, ent = i32([ctx] * B), i32(list(range(B + 1))), i32(list(range(B)))
+    table = torch.randperm(B * blocks, device=dev).to(torch.int32).view(B, blocks).contiguous()
+    lh, lkv, lhd = sz["llama"]
+
+    def single(Hq, Hkv, hd, vd, maps, vik, window, softcap, sink_values):
+        att = PlainAttend(bctx, Hq, Hkv, hd, vd, maps=maps, value_in_key=vik, window=window)
+        per = Hkv * maps * hd + (0 if vik else Hkv * vd)
+        cache = bf(B * blocks, PAGE * per)
+        q = bf(B, Hq * hd)
+        o = torch.empty(B, Hq * vd, device=dev, dtype=torch.float32 if maps > 1 else torch.bfloat16)
+        span = min(ctx, window) if window else ctx
+        if att.fast_single:
+            ranges = att._splits(B, ctx)
+            us = time_kernel(lambda: K.attention_single(q, o, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
+                                                        sink=sink_values is not None, splits=ranges, part=att.part, softcap=softcap,
+                                                        sink_values=sink_values, maps=maps, value_in_key=vik), flush=flush)
+        else:
+            ranges = 0
+            t0 = i32([0] * B)
+            us = time_kernel(lambda: K.attention_plain(q, o, cache, table, cu, kv_len, ent, t0, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
+                                                       sink=sink_values is not None, softcap=softcap, sink_values=sink_values,
+                                                       maps=maps, value_in_key=vik), repeats=5, flush=flush)
+        return {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(B * span * per * 2, us),
+                "kernel": "one CTA a key head" if att.fast_single else "tiles of 16 rows a head"}
+    res = single(2 * ah, akv, ad, av, 2, False, win, 50.0, None)
+    like = single(lh, lkv, lhd, lhd, 1, False, win, None, torch.zeros(lh, device=dev))
+    res.update(window_sink_us=like["us"], window_sink_hbm_frac=like["hbm_frac"])
+    out["two_map_attention_decode64"] = res
+    res = single(th, 1, kd, rank, 1, True, None, None, torch.zeros(th, device=dev))
+    like = single(lh, lkv, lhd, lhd, 1, False, None, None, torch.zeros(lh, device=dev))
+    res.update(causal_sink_us=like["us"], causal_sink_hbm_frac=like["hbm_frac"])
+    out["latent_attention_decode64"] = res
+    # a prompt of 2,048 tokens: the fp32-arithmetic tiles beside Pikalix's tensor-core kernel with fp32 weights
+    T = 2048
+    tbl = i32([list(range(T // PAGE))])
+    cup, kvl = i32([0, T]), i32([T])
+    tiles = list(range(0, T, 16))
+    te, t0 = i32([0] * len(tiles)), i32(tiles)
+
+    def prompt(Hq, Hkv, hd, vd, maps, vik, window, softcap, sink_values):
+        per = Hkv * maps * hd + (0 if vik else Hkv * vd)
+        cache = bf(T // PAGE, PAGE * per)
+        q = bf(T, Hq * hd)
+        o = torch.empty(T, Hq * vd, device=dev, dtype=torch.float32 if maps > 1 else torch.bfloat16)
+        us = time_kernel(lambda: K.attention_plain(q, o, cache, tbl, cup, kvl, te, t0, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
+                                                   sink=sink_values is not None, softcap=softcap, sink_values=sink_values, maps=maps,
+                                                   value_in_key=vik), repeats=5, flush=flush)
+        pairs = sum(min(p + 1, window) if window else p + 1 for p in range(T))
+        return {"us": round(us, 1), "tflops": round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2),
+                "fma_frac": round(pairs * Hq * (hd + vd) / (us * 1e-6) / fma_per_s, 4)}
+    res = prompt(2 * ah, akv, ad, av, 2, False, win, 50.0, None)
+    pcache = bf(T // PAGE, 2, lkv, PAGE, lhd)
+    qp, op = bf(T, lh * lhd), torch.empty(T, lh * lhd, device=dev, dtype=torch.bfloat16)
+    rows = K.mma_tokens_per_tile(lh, lkv)
+    tl = list(range(0, T, rows))
+    te1, t01 = i32([0] * len(tl)), i32(tl)
+    for name, w_ in (("window", win), ("causal", None)):
+        pairs = sum(min(p + 1, w_) if w_ else p + 1 for p in range(T))
+        us1 = time_kernel(lambda: K.attention_prefill_bf16(qp, op, pcache, tbl, cup, kvl, te1, t01, lh, lkv, lhd, lhd ** -0.5, w_, None,
+                                                           precise=True, sink=True), flush=flush)
+        like = {f"{name}_sink_mma_us": round(us1, 1), f"{name}_sink_mma_useful_tflops": round(2 * pairs * lh * 2 * lhd / (us1 * 1e-6) / 1e12, 2)}
+        if name == "window":
+            res.update(like)
+            out["two_map_attention_prefill2048"] = res
+            res = prompt(th, 1, kd, rank, 1, True, None, None, torch.zeros(th, device=dev))
+        else:
+            res.update(like)
+            out["latent_attention_prefill2048"] = res
+    return out
+
+
 def family_bench(args) -> int:
-    """`--family dirurax|pikalix`: prefill and decode throughput of that family's models at a few sizes beside
+    """`--family dirurax|pikalix|sotazen`: prefill and decode throughput of that family's models at a few sizes beside
     Llama models of the same width, depth, feed-forward width and vocabulary (random weights), and the
     family's own kernels alone.  One JSON line."""
     import torch
@@ -778,13 +983,15 @@ def family_bench(args) -> int:
     say = lambda msg: print(f"[bench] {msg}", file=sys.stderr, flush=True)
     ctx, tokens = min(args.context, 4096), max(2, min(args.prompt_tokens, 8192))
     family = args.family
-    table = PIKALIX_SIZES if family == "pikalix" else FAMILY_SIZES
+    table = {"pikalix": PIKALIX_SIZES, "sotazen": SOTAZEN_SIZES}.get(family, FAMILY_SIZES)
     result = {"family": family, "dtype": "bf16", "data": "synthetic", "peaks": peak_kind, "points": {}, "kernels": {}}
     sizes = [s for s in table if not args.size or s in args.size.split(",")]
     for size in sizes:
         sz = table[size]
         if family == "pikalix":
             own = _pikalix(**{k: v for k, v in sz.items() if k != "llama"})
+        elif family == "sotazen":
+            own = _sotazen(**{k: v for k, v in sz.items() if k != "llama"})
         else:
             own = _dirurax(sz["width"], sz["layers"], sz["ff"], sz["vocab"], sz["gla"], sz["attn"], sz["delta"], sz["block"])
         configs = {family: own, "llama": _llama_like(sz["width"], sz["layers"], sz["ff"], sz["vocab"], *sz["llama"])}
@@ -816,6 +1023,7 @@ def family_bench(args) -> int:
         point["decode_ratio"] = round(point[family]["decode_tokens_per_s"] / point["llama"]["decode_tokens_per_s"], 3)
         result["points"][size] = point
         result["kernels"][size] = (pikalix_kernels(hbm_gbs, bf16_tflops, size) if family == "pikalix"
+                                   else sotazen_kernels(hbm_gbs, bf16_tflops, size) if family == "sotazen"
                                    else dirurax_kernels(hbm_gbs, size))
         say(f"{size} kernels: {result['kernels'][size]}")
     clocks.stop()
@@ -850,7 +1058,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
-    ap.add_argument("--family", default="llama", choices=["llama", "dirurax", "pikalix"],
+    ap.add_argument("--family", default="llama", choices=["llama", "dirurax", "pikalix", "sotazen"],
                     help="dirurax, pikalix: that family's prefill and decode at a few sizes beside Llama models of equal size, "
                          "and its kernels alone (one JSON line of its own; the default workload is unchanged)")
     ap.add_argument("--size", default="", help="with --family dirurax or pikalix: sizes to run, with commas (default: all)")
@@ -865,7 +1073,7 @@ def main() -> int:
         return 0
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 2)
-    if args.family in ("dirurax", "pikalix"):
+    if args.family in ("dirurax", "pikalix", "sotazen"):
         return family_bench(args)
 
     import torch

@@ -45,7 +45,9 @@ def _layer(mixer, ff=None):
 #    than values and a decay close to one; attention with as many kv heads as heads, no rotation, a window equal
 #    to the page
 # C: one head everywhere it can be; a lightning layer first; attention with a window of 9 inside one page and no
-#    feed-forward; a latent layer of three heads with a rotated part of four channels; alpha below one
+#    feed-forward (its `diff` small: with scores capped at 1.5 the two maps are nearly alike, and a weight near one on
+#    the second would leave a difference that is mostly rounding in bfloat16); a latent layer of three heads with a
+#    rotated part of four channels; alpha below one
 CONFIGS = {
     "A": {"architecture": "Sotazen", "width": 96, "vocab": 211, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.7},
           "postln_alpha": 2.0, "layers": [
@@ -60,7 +62,7 @@ CONFIGS = {
     "C": {"architecture": "Sotazen", "width": 64, "vocab": 97, "norm": {"eps": 3e-6}, "embedding": {"scale": 2.0},
           "postln_alpha": 0.5, "layers": [
               _layer(_lightning(1, 20, 12, [0.95]), 72),
-              _layer(_att(1, 1, 40, 8, 0.25, 0.6, mask=9, rot=(20, 1e6), softcap=1.5)),
+              _layer(_att(1, 1, 40, 8, 0.25, 0.15, mask=9, rot=(20, 1e6), softcap=1.5)),
               _layer(_latent(3, 20, 4, 36, 20, 0.35, 50.0), 80)]},
 }
 
