@@ -910,18 +910,18 @@ def sotazen_kernels(hbm_gbs, bf16_tflops, size):
         o = torch.empty(B, Hq * vd, device=dev, dtype=torch.float32 if maps > 1 else torch.bfloat16)
         span = min(ctx, window) if window else ctx
         if att.fast_single:
-            ranges = att._splits(B, ctx)
+            ranges, kernel = att._splits(B, ctx), "one CTA a key head"
             us = time_kernel(lambda: K.attention_single(q, o, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
                                                         sink=sink_values is not None, splits=ranges, part=att.part, softcap=softcap,
                                                         sink_values=sink_values, maps=maps, value_in_key=vik), flush=flush)
         else:
-            ranges = 0
-            t0 = i32([0] * B)
-            us = time_kernel(lambda: K.attention_plain(q, o, cache, table, cu, kv_len, ent, t0, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
-                                                       sink=sink_values is not None, softcap=softcap, sink_values=sink_values,
-                                                       maps=maps, value_in_key=vik), repeats=5, flush=flush)
-        return {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(B * span * per * 2, us),
-                "kernel": "one CTA a key head" if att.fast_single else "tiles of 16 rows a head"}
+            ranges, t0 = 0, i32([0] * B)
+            fn, kernel = ((K.attention_rows, "tensor cores, 64 (token, head) rows a CTA") if att.rows else
+                          (lambda *a, **k: K.attention_plain(*a[:13], None, *a[13:], **k), "fp32 arithmetic, 16 rows a head"))
+            us = time_kernel(lambda: fn(q, o, cache, table, cu, kv_len, ent, t0, Hq, Hkv, hd, hd ** -0.5, window, vd,
+                                        sink=sink_values is not None, softcap=softcap, sink_values=sink_values,
+                                        maps=maps, value_in_key=vik), repeats=5, flush=flush)
+        return {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(B * span * per * 2, us), "kernel": kernel}
     res = single(2 * ah, akv, ad, av, 2, False, win, 50.0, None)
     like = single(lh, lkv, lhd, lhd, 1, False, win, None, torch.zeros(lh, device=dev))
     res.update(window_sink_us=like["us"], window_sink_hbm_frac=like["hbm_frac"])
@@ -942,12 +942,20 @@ def sotazen_kernels(hbm_gbs, bf16_tflops, size):
         cache = bf(T // PAGE, PAGE * per)
         q = bf(T, Hq * hd)
         o = torch.empty(T, Hq * vd, device=dev, dtype=torch.float32 if maps > 1 else torch.bfloat16)
-        us = time_kernel(lambda: K.attention_plain(q, o, cache, tbl, cup, kvl, te, t0, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
-                                                   sink=sink_values is not None, softcap=softcap, sink_values=sink_values, maps=maps,
-                                                   value_in_key=vik), repeats=5, flush=flush)
+        opts = dict(sink=sink_values is not None, softcap=softcap, sink_values=sink_values, maps=maps, value_in_key=vik)
+        us32 = time_kernel(lambda: K.attention_plain(q, o, cache, tbl, cup, kvl, te, t0, Hq, Hkv, hd, hd ** -0.5, window, None, vd, **opts),
+                           repeats=5, flush=flush)
         pairs = sum(min(p + 1, window) if window else p + 1 for p in range(T))
-        return {"us": round(us, 1), "tflops": round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2),
-                "fma_frac": round(pairs * Hq * (hd + vd) / (us * 1e-6) / fma_per_s, 4)}
+        res = {"fp32_arithmetic_us": round(us32, 1), "fp32_arithmetic_fma_frac": round(pairs * Hq * (hd + vd) / (us32 * 1e-6) / fma_per_s, 4)}
+        if K.attention_rows_supports(hd, vd, vik):
+            tpt = K.attention_rows_tokens_per_tile(Hq, Hkv, hd, vd, maps)
+            tl = list(range(0, T, tpt))
+            ter, t0r = i32([0] * len(tl)), i32(tl)
+            us = time_kernel(lambda: K.attention_rows(q, o, cache, tbl, cup, kvl, ter, t0r, Hq, Hkv, hd, hd ** -0.5, window, vd, **opts),
+                             flush=flush)
+            res.update(us=round(us, 1), useful_tflops=round(2 * pairs * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2),
+                       tflops=round(2 * pairs * Hq * (hd + 3 * vd) / (us * 1e-6) / 1e12, 2))
+        return res
     res = prompt(2 * ah, akv, ad, av, 2, False, win, 50.0, None)
     pcache = bf(T // PAGE, 2, lkv, PAGE, lhd)
     qp, op = bf(T, lh * lhd), torch.empty(T, lh * lhd, device=dev, dtype=torch.bfloat16)

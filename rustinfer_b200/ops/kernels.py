@@ -475,6 +475,45 @@ def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
           "attention_single", 2 if splits > 1 else 1)
 
 
+def attention_rows_supports(head_dim: int, value_dim: int, value_in_key: bool = False) -> bool:
+    """Whether `attention_rows` takes keys of `head_dim` and values of `value_dim` (multiples of 16, keys up to 576,
+    values up to 256; values inside the keys are no wider than the keys)."""
+    return L.attention_rows_supports(head_dim, value_dim, value_in_key)
+
+
+def attention_rows_tokens_per_tile(num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, maps: int = 1) -> int:
+    """Tokens of one tile of `attention_rows`: 64 rows over the query heads that share a key head."""
+    n = int(L.attention_rows(head_dim, value_dim).ri_attention_rows_tokens_per_tile(num_heads, num_kv_heads, maps))
+    if n <= 0:
+        raise KernelError("attention_rows: heads (with their maps) must be a multiple of kv heads times maps")
+    return n
+
+
+def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                   cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor, tile_tok0: torch.Tensor,
+                   num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                   value_dim: Optional[int] = None, sink: bool = False, softcap: Optional[float] = None,
+                   sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
+    """`attention_plain` on the tensor cores for a bf16 cache: the scores are fp32 sums of products of bf16 q and
+    k, cap, mask and softmax are fp32, and the softmax weights meet the bf16 values unrounded (three bf16 pieces a
+    weight).  Arguments as there, without `block`; tiles hold `attention_rows_tokens_per_tile` tokens."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0, sink_values)
+    for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
+                 (tile_entry, "tile_entry"), (tile_tok0, "tile_tok0")):
+        _i32(t, n)
+    vd = value_dim or head_dim
+    if cache.dtype != torch.bfloat16 or q.stride(0) % 8 or q.data_ptr() % 16 or cache.data_ptr() % 16:
+        raise KernelError("attention_rows: a bf16 cache and q rows that start on 16-byte boundaries")
+    if out.dtype == torch.float32 and (out.stride(0) % 2 or out.data_ptr() % 8):
+        raise KernelError("attention_rows: fp32 out rows start on 8-byte boundaries")
+    page_size = _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key)
+    check(L.attention_rows(head_dim, vd).ri_attention_rows(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(cu_q),
+        _p(kv_len), _p(tile_entry), _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads, page_size, float(scale),
+        int(window) if window else 0, 1 if sink else 0, float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
+        1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()), "attention_rows")
+
+
 def attention_single_scratch_floats(entries: int, num_heads: int, value_dim: int, splits: int) -> int:
     return entries * num_heads * splits * (value_dim + 2)
 

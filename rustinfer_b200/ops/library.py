@@ -45,6 +45,8 @@ _SIGNATURES = {
     "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "ri_attention_plain_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _I, _P],
     "ri_attention_single_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _F, _P, _I, _I, _I, _P],
+    "ri_attention_rows": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _F, _P, _I, _I, _I, _P],
+    "ri_attention_rows_tokens_per_tile": [_I, _I, _I],
     "ri_embed_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_round_rows": [_P, _P, _I, _L, _P],
     "ri_scale_add_norm": [_P, _P, _I, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
@@ -129,6 +131,24 @@ def attention_plain(head_dim: int, value_dim: Optional[int] = None) -> ctypes.CD
     if value_dim == head_dim:
         return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
     return _load(f"ri_attention_plain_hd{head_dim}_vd{value_dim}", ["attention_plain.cu"],
+                 [f"RI_HEAD_DIM={head_dim}", f"RI_VALUE_DIM={value_dim}"])
+
+
+ROWS_MAX_HEAD_DIM, ROWS_MAX_VALUE_DIM = 576, 256
+
+
+def attention_rows_supports(head_dim: int, value_dim: int, value_in_key: bool = False) -> bool:
+    """Whether the tensor-core attention for keys and values of different sizes takes this geometry."""
+    return (head_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= head_dim <= ROWS_MAX_HEAD_DIM
+            and 16 <= value_dim <= ROWS_MAX_VALUE_DIM and (not value_in_key or value_dim <= head_dim))
+
+
+def attention_rows(head_dim: int, value_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention with fp32 softmax weights for keys of `head_dim` and values of `value_dim`."""
+    if not attention_rows_supports(head_dim, value_dim):
+        raise KernelError(f"the tensor-core attention for unequal sizes takes multiples of 16 up to {ROWS_MAX_HEAD_DIM} "
+                          f"(keys) and {ROWS_MAX_VALUE_DIM} (values), got {head_dim} and {value_dim}")
+    return _load(f"ri_attention_rows_hd{head_dim}_vd{value_dim}", ["attention_rows.cu"],
                  [f"RI_HEAD_DIM={head_dim}", f"RI_VALUE_DIM={value_dim}"])
 
 

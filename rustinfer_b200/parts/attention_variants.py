@@ -26,11 +26,12 @@ from .spec import PartSpec
 
 
 class PlainAttend:
-    """How a mixer sends its queries to the fp32-arithmetic kernels: entries of one token to the kernel
-    that reads a key head once for all its query heads (bfloat16 engine, where it takes the geometry;
-    the keys cut into ranges when few CTAs would walk many keys), everything else in tiles of 16 query
-    rows.  The 32-bit engine uses the tiled kernel alone, whose sums do not depend on how the tokens
-    were cut into steps."""
+    """How a mixer sends its queries to the attention kernels with fp32 scores and softmax weights.  The bfloat16
+    engine: entries of one token go to the kernel that reads a key head once for all its query heads (where it
+    takes the geometry; the keys cut into ranges when few CTAs would walk many keys), everything else to the
+    tensor-core kernel in tiles of 64 (token, head) rows (where the sizes are multiples of 16), and what neither
+    takes to the fp32-arithmetic kernel in tiles of 16 query rows.  The 32-bit engine uses that last kernel alone,
+    whose sums do not depend on how the tokens were cut into steps."""
     MAX_SPLITS = 16
 
     def __init__(self, ctx: BuildContext, heads: int, kv_heads: int, head_dim: int, value_dim: int, maps: int = 1,
@@ -40,9 +41,11 @@ class PlainAttend:
         self.value_in_key, self.window = value_in_key, window
         fast = (ctx.dtype == torch.bfloat16 and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "fast") != "plain")
         self.fast_single = fast and K.attention_single_supports(heads, kv_heads, head_dim, value_dim, maps)
+        self.rows = fast and K.attention_rows_supports(head_dim, value_dim, value_in_key)
+        rows = K.attention_rows_tokens_per_tile(heads, kv_heads, head_dim, value_dim, maps) if self.rows else 16
         if self.fast_single:
             self._single = single_token_entries()
-            self._tiles = token_tiles(16, skip_single_token=True)
+            self._tiles = token_tiles(rows, skip_single_token=True)
             key = ("single_scratch", heads, value_dim)
             if key not in ctx.shared:
                 n = K.attention_single_scratch_floats(ctx.max_batch_seqs, heads, value_dim, self.MAX_SPLITS)
@@ -50,7 +53,7 @@ class PlainAttend:
             self.part = ctx.shared[key]
         else:
             self._single = None
-            self._tiles = token_tiles(16, skip_single_token=False)
+            self._tiles = token_tiles(rows, skip_single_token=False)
 
     def step_indices(self):
         return [self._tiles] if self._single is None else [self._single, self._tiles]
@@ -73,8 +76,12 @@ class PlainAttend:
                                    part=self.part, **opts)
         tile_entry, tile_tok0 = step.index(self._tiles)
         if tile_entry.numel():
-            K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
-                              self.Hq, self.Hkv, self.hd, scale, self.window, None, **opts)
+            if self.rows:
+                K.attention_rows(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
+                                 self.Hq, self.Hkv, self.hd, scale, self.window, **opts)
+            else:
+                K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
+                                  self.Hq, self.Hkv, self.hd, scale, self.window, None, **opts)
         return out
 
 

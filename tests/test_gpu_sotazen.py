@@ -362,7 +362,7 @@ def test_two_map_attention_edges_and_far_keys(dk, dv, window, cap):
 
 
 # ------------------------------------------------------------ attention over one cached row a token, with a sink
-@pytest.mark.parametrize("rank,r,H", [(40, 8, 4), (48, 16, 2), (20, 4, 3), (96, 16, 8)])
+@pytest.mark.parametrize("rank,r,H", [(40, 8, 4), (48, 16, 2), (20, 4, 3), (88, 16, 6)])
 def test_latent_rows_attention_far_keys_and_sink(rank, r, H):
     """One row [low-rank vector, shared key part] a token is every head's key, and its first `rank` channels
     the value.  One key stands out with score 0: a head whose sink is 0 gives it the weight 1/2, a head whose
@@ -430,6 +430,126 @@ def test_latent_rows_attention_far_keys_and_sink(rank, r, H):
         if K().attention_single_supports(H, 1, kd, rank):
             for splits in (1, 2, 5):
                 assert float((attend_single(p, tgt, splits).to(F64) - ref).abs().max()) < 2e-4, (p, tgt, splits)
+
+
+# ------------------------------------------------------------ the same two attentions on the tensor cores
+BF = torch.bfloat16
+
+
+def bf_round(x):
+    return x.to(BF).to(torch.float32)
+
+
+@pytest.mark.parametrize("dk,dv,H,G,window,cap", [(15, 32, 4, 2, 20, 20.0), (31, 16, 6, 1, 16, None), (47, 80, 4, 1, 24, 45.0),
+                                                  (63, 128, 2, 2, None, 30.0)])
+def test_two_map_attention_on_tensor_cores(dk, dv, H, G, window, cap):
+    """`attention_rows` against the plain model on inputs that bfloat16 holds exactly: for every query and map one
+    key stands out, just inside and just outside the window, in prompt portions (from the first token on, and from
+    the middle of a page) and for single tokens, pages scrambled and poisoned outside; without a window a key
+    hundreds of tokens back."""
+    page, n = 8, 330
+    table = torch.randperm(48, generator=torch.Generator().manual_seed(5)).tolist()[: (n + page - 1) // page]
+    unit = torch.nn.functional.normalize(rnd(n, 2, dk, seed=2), dim=-1)
+    top = max(float((unit[:, m] @ unit[:, m].T - 2.0 * torch.eye(n)).max()) for m in range(2))
+    gain = 30.0 / (1.0 - top)
+    keys = bf_round(torch.cat([unit, torch.ones(n, 2, 1)], dim=-1))[:, None].repeat(1, G, 1, 1)    # [n, G, 2, dk+1]
+    vals = bf_round(rnd(n, G, dv, seed=1))
+    d1 = dk + 1
+    cache = paged_maps(keys, vals, page, table, BF)
+    bt = i32([table])
+    tpt = K().attention_rows_tokens_per_tile(2 * H, G, d1, dv, 2)
+    assert tpt == 64 // (H // G)
+
+    def queries(targets):
+        q = torch.zeros(len(targets), H, 2, d1)
+        for i, tg in enumerate(targets):
+            for m in range(2):
+                q[i, :, m, :dk] = unit[tg[m], m] * gain
+                q[i, :, m, dk] = -gain
+        return bf_round(q)
+
+    def plain_rows(first, targets):
+        T = first + len(targets)
+        q = torch.zeros(T, H, 2, d1, dtype=F64)
+        q[first:] = queries(targets).to(F64)
+        return P.two_map_attention(q, keys[:T].to(F64), vals[:T].to(F64), 1.0, cap, window)[first:]
+
+    def attend(first, targets):
+        count = len(targets)
+        out = torch.full((count, H * 2 * dv), float("nan"), dtype=torch.float32, device=DEV)
+        tiles = list(range(0, count, tpt))
+        K().attention_rows(queries(targets).reshape(count, -1).to(BF).to(DEV), out, cache, bt, i32([0, count]),
+                           i32([first + count]), i32([0] * len(tiles)), i32(tiles), 2 * H, G, d1, 1.0, window, dv,
+                           softcap=cap, maps=2)
+        return out.cpu().view(count, H, 2, dv)
+
+    w = window or 10 ** 9
+    for first, count in ((45, 70), (0, 67), (128, 1)):
+        for shift in ((0, 1, w - 1, w, w + 1) if window else (0, 1, 40, 100)):
+            other = max(0, shift - 3)
+            targets = [(max(0, p - shift), max(0, p - other)) for p in range(first, first + count)]
+            got, ref = attend(first, targets), plain_rows(first, targets)
+            assert float((got.to(F64) - ref).abs().max()) < 2e-4, (first, shift)
+            for m, sh in ((0, shift), (1, other)):
+                if targets[-1][m] == first + count - 1 - sh:           # not clamped at the first token
+                    lead = float((ref[-1, 0, m] - vals[targets[-1][m], 0].to(F64)).abs().max())
+                    assert (lead < 1e-2) == (sh < w), (first, shift, m)
+    for p, tgt in [(n - 1, 3), (n - 1, n - 1), (300, 0), (64, 63), (7, 0), (0, 0)]:
+        tg = (tgt, min(p, tgt + 1))
+        assert float((attend(p, [tg])[0].to(F64) - plain_rows(p, [tg])[0]).abs().max()) < 2e-4, (p, tgt)
+
+
+@pytest.mark.parametrize("rank,r,H", [(32, 16, 4), (80, 16, 3), (64, 48, 20), (16, 16, 70), (256, 32, 8)])
+def test_latent_rows_attention_on_tensor_cores(rank, r, H):
+    """`attention_rows` over one cached row a token with a sink a head: 3, 20 and 70 heads on one key head (a tile
+    of 64 rows then holds 21, 3 and 1 tokens; 70 heads take two CTAs), a key 326 tokens back among hundreds."""
+    page, n = 8, 330
+    kd = rank + r
+    table = torch.randperm(48, generator=torch.Generator().manual_seed(7)).tolist()[: (n + page - 1) // page]
+    unit = torch.nn.functional.normalize(rnd(n, kd - 1, seed=2), dim=-1)
+    gain = 30.0 / (1.0 - float((unit @ unit.T - 2.0 * torch.eye(n)).max()))
+    rows = bf_round(torch.cat([unit, torch.ones(n, 1)], dim=-1))
+    cache = torch.full((max(table) + 2, page * kd), 1e4)
+    for t in range(n):
+        cache[table[t // page], (t % page) * kd: (t % page + 1) * kd] = rows[t]
+    cache = cache.to(BF).to(DEV)
+    bt = i32([table])
+    sink = torch.tensor(([0.0, -1e4, 40.0, 1.0] * 18)[:H])
+    tpt = K().attention_rows_tokens_per_tile(H, 1, kd, rank, 1)
+    assert tpt == max(1, 64 // H)
+
+    def queries(targets):
+        q = torch.zeros(len(targets), H, kd)
+        for i, tgt in enumerate(targets):
+            q[i, :, : kd - 1] = unit[tgt] * gain
+            q[i, :, kd - 1] = -gain
+        return bf_round(q)
+
+    def plain_rows(first, targets):
+        T = first + len(targets)
+        q = torch.zeros(T, H, kd, dtype=F64)
+        q[first:] = queries(targets).to(F64)
+        sc = torch.einsum("ihd,jd->hij", q, rows[:T].to(F64)) * 0.5
+        p = P.softmax_rows(sc, P.visible(T, None), sink.to(F64))
+        return torch.einsum("hij,jv->ihv", p, rows[:T, :rank].to(F64))[first:]
+
+    def attend(first, targets, dtype=torch.float32):
+        count = len(targets)
+        out = torch.full((count, H * rank), float("nan"), dtype=dtype, device=DEV)
+        tiles = list(range(0, count, tpt))
+        K().attention_rows(queries(targets).reshape(count, -1).to(BF).to(DEV), out, cache, bt, i32([0, count]),
+                           i32([first + count]), i32([0] * len(tiles)), i32(tiles), H, 1, kd, 0.5, None, rank,
+                           sink=True, sink_values=sink.to(DEV), value_in_key=True)
+        return out.float().cpu().view(count, H, rank)
+
+    for first, count in ((45, 70), (0, 33)):
+        for shift in (0, 1, 40, 100):
+            targets = [max(0, p - shift) for p in range(first, first + count)]
+            got, ref = attend(first, targets), plain_rows(first, targets)
+            assert float((got.to(F64) - ref).abs().max()) < 2e-4, (first, shift)
+    assert float((attend(45, list(range(45, 115)), BF).to(F64) - plain_rows(45, list(range(45, 115)))).abs().max()) < 1e-2
+    for p, tgt in [(n - 1, 3), (n - 1, n - 1), (300, 0), (64, 63), (7, 0), (0, 0)]:
+        assert float((attend(p, [tgt])[0].to(F64) - plain_rows(p, [tgt])[0]).abs().max()) < 2e-4, (p, tgt)
 
 
 # ============================================================================ the engine
