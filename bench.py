@@ -1,4 +1,4 @@
-"""Decode and prefill throughput of the engine on one B200, in the contract's one JSON line.
+"""Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--shape 1b|3b|8b]
 
@@ -914,6 +914,12 @@ def sotazen_kernels(hbm_gbs, bf16_tflops, size):
             us = time_kernel(lambda: K.attention_single(q, o, cache, table, cu, kv_len, ent, Hq, Hkv, hd, hd ** -0.5, window, None, vd,
                                                         sink=sink_values is not None, splits=ranges, part=att.part, softcap=softcap,
                                                         sink_values=sink_values, maps=maps, value_in_key=vik), flush=flush)
+        elif att.rows_single:
+            ranges, kernel = att._rows_splits(B, ctx), "tensor cores, 64 (token, head) rows a CTA"
+            us = time_kernel(lambda: K.attention_rows(q, o, cache, table, cu, kv_len, ent, att.zero_tok0[:B], Hq, Hkv, hd, hd ** -0.5,
+                                                      window, vd, sink=sink_values is not None, softcap=softcap,
+                                                      sink_values=sink_values, maps=maps, value_in_key=vik, splits=ranges,
+                                                      part=att.part), flush=flush)
         else:
             ranges, t0 = 0, i32([0] * B)
             fn, kernel = ((K.attention_rows, "tensor cores, 64 (token, head) rows a CTA") if att.rows else
@@ -921,14 +927,15 @@ def sotazen_kernels(hbm_gbs, bf16_tflops, size):
             us = time_kernel(lambda: fn(q, o, cache, table, cu, kv_len, ent, t0, Hq, Hkv, hd, hd ** -0.5, window, vd,
                                         sink=sink_values is not None, softcap=softcap, sink_values=sink_values,
                                         maps=maps, value_in_key=vik), repeats=5, flush=flush)
-        return {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(B * span * per * 2, us), "kernel": kernel}
+        return {"us": round(us, 1), "ranges": ranges, "hbm_frac": frac(B * span * per * 2, us), "kernel": kernel,
+                "useful_tflops": round(2 * B * span * Hq * (hd + vd) / (us * 1e-6) / 1e12, 2)}
     res = single(2 * ah, akv, ad, av, 2, False, win, 50.0, None)
     like = single(lh, lkv, lhd, lhd, 1, False, win, None, torch.zeros(lh, device=dev))
     res.update(window_sink_us=like["us"], window_sink_hbm_frac=like["hbm_frac"])
     out["two_map_attention_decode64"] = res
     res = single(th, 1, kd, rank, 1, True, None, None, torch.zeros(th, device=dev))
     like = single(lh, lkv, lhd, lhd, 1, False, None, None, torch.zeros(lh, device=dev))
-    res.update(causal_sink_us=like["us"], causal_sink_hbm_frac=like["hbm_frac"])
+    res.update(causal_sink_us=like["us"], causal_sink_hbm_frac=like["hbm_frac"], causal_sink_useful_tflops=like["useful_tflops"])
     out["latent_attention_decode64"] = res
     # a prompt of 2,048 tokens: the fp32-arithmetic tiles beside Pikalix's tensor-core kernel with fp32 weights
     T = 2048

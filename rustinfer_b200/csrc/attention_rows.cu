@@ -14,7 +14,10 @@
 // that start at multiples of KT from key 0 (the sums' order does not depend on how a prompt was cut), gathered page
 // by page with cp.async into a double buffer.  Options as in the fp32-arithmetic kernel: `maps` attention maps a
 // head (query heads [head][map], key heads [kv head][map], one set of values), values that are the keys' own first
-// channels, a window, a term exp(sink_h) in the denominator, fp32 or bf16 output.  The reference has one
+// channels, a window, a term exp(sink_h) in the denominator, fp32 or bf16 output.  With `splits` > 1 the key tiles of
+// every CTA are cut into that many ranges, a CTA each (grid z), which leave their unnormalised sums, maximum and sum
+// in a scratch; a second kernel joins them.  That is for steps of few tiles over many keys (single tokens of a long
+// context), where one CTA a tile would leave most SMs idle.  The reference has one
 // attention kernel pair for one head size (crates/infer-backend-cuda/src/kernels/flash_attn_gqa/flash_attn_gqa.h:30).
 #include "common.cuh"
 
@@ -76,6 +79,7 @@ struct Geometry {
     int page_size;
     int window;            // 0: every earlier key
     int sink;              // the denominator holds exp(sink_values[h]) (null: exp(0)) besides the keys' terms
+    int splits;            // ranges the key tiles of a CTA are cut into (grid z); > 1: results go through `part`
     float scale, softcap;  // softcap 0: scores are not capped
 };
 
@@ -107,7 +111,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
                       const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                       const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                       const int* __restrict__ tile_entry, const int* __restrict__ tile_tok0,
-                      const float* __restrict__ sink_values, Geometry gm) {
+                      const float* __restrict__ sink_values, float* __restrict__ part, Geometry gm) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -143,13 +147,20 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
 
     const int p_first = pos0 + tok0, p_last = p_first + ntok - 1;
     const int lo_tile = gm.window > 0 ? max(0, p_first - gm.window + 1) : 0;
-    const int t_begin = lo_tile / KT, t_end = p_last / KT + 1;
+    int t_begin = lo_tile / KT, t_end = p_last / KT + 1;
+    if (gm.splits > 1) {
+        // this CTA's range of the key tiles; it may be empty
+        const int per = (t_end - t_begin + gm.splits - 1) / gm.splits;
+        t_begin += blockIdx.z * per;
+        t_end = min(t_end, t_begin + per);
+    }
     const int* bt = block_table + (size_t)b * table_stride;
     const size_t page_elems = (size_t)gm.page_size * ((size_t)Hk * HD + (VIK ? 0 : (size_t)gm.Hkv * VD));
     const size_t k_base = (size_t)kh * gm.page_size * HD;
     const size_t v_base = (size_t)Hk * gm.page_size * HD + (size_t)kvh * gm.page_size * VD;
 
-    load_tile<VIK>(KVs, KVs + KT * KROW, cache, bt, t_begin * KT, lo_tile, p_last + 1, page_elems, k_base, v_base, gm.page_size);
+    if (t_begin < t_end)
+        load_tile<VIK>(KVs, KVs + KT * KROW, cache, bt, t_begin * KT, lo_tile, p_last + 1, page_elems, k_base, v_base, gm.page_size);
     cp_async_commit();
     __syncthreads();                                          // Qs is written
 
@@ -165,7 +176,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
         p_row[i] = p_first + jj;
         lo_row[i] = gm.window > 0 ? max(0, p_row[i] - gm.window + 1) : 0;
         m[i] = -INFINITY;
-        if (gm.sink && ok_row[i]) {
+        if (gm.sink && gm.splits == 1 && ok_row[i]) {           // with ranges, the join adds the term once
             // a term exp(sink_h) without a value: the maximum starts there and, in the one lane of four whose
             // partial sum stands for it, the sum at exp(sink_h - sink_h) = 1
             m[i] = (sink_values ? sink_values[head_of(hh)] : 0.f) * LOG2E;
@@ -290,6 +301,14 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
         if (!ok_row[i]) continue;
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         const int jj = r / Gc, hh = r - jj * Gc;
+        if (gm.splits > 1) {
+            float* dst = part + ((((size_t)blockIdx.x * gridDim.y + blockIdx.y) * MT + r) * gm.splits + blockIdx.z) * (VD + 2);
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8 + (lane & 3) * 2) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
+            if ((lane & 3) == 0) { dst[VD] = m[i]; dst[VD + 1] = l[i]; }
+            continue;
+        }
         const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
         TO* dst = out + (size_t)(q_begin + tok0 + jj) * out_stride + (size_t)head_of(hh) * VD + (lane & 3) * 2;
 #pragma unroll
@@ -303,10 +322,80 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
     }
 }
 
+// Joins the ranges of one row of a tile, a warp a row: M = the largest maximum (the sink's exponent among them),
+// L = sum l_z 2^(m_z - M) (+ 2^(sink - M)), out = sum acc_z 2^(m_z - M) / L; maxima are in units of log2.  Lane z
+// holds range z's weight 2^(m_z - M) (ranges beyond 32 in a second turn); the sums run over the ranges in their order.
+constexpr int MERGE_WARPS = 4;
+template <typename TO>
+__global__ void __launch_bounds__(MERGE_WARPS * 32)
+attention_rows_merge_kernel(const float* __restrict__ part, TO* __restrict__ out, int out_stride,
+                            const int* __restrict__ cu_q, const int* __restrict__ tile_entry,
+                            const int* __restrict__ tile_tok0, const float* __restrict__ sink_values, Geometry gm) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = tile_entry[blockIdx.x];
+    if (b < 0) return;
+    const int tok0 = tile_tok0[blockIdx.x];
+    const int Hk = gm.Hkv * gm.maps, G = gm.Hq / Hk, Gc = gm.Gc;
+    const int kh = blockIdx.y / gm.chunks, hc = blockIdx.y - kh * gm.chunks;
+    const int kvh = kh / gm.maps, mp = kh - kvh * gm.maps;
+    const int g0 = hc * Gc, nheads = min(Gc, G - g0);
+    const int q_begin = cu_q[b], ntok = min(gm.tpt, cu_q[b + 1] - q_begin - tok0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.z * MERGE_WARPS + warp;
+    const int jj = r / Gc, hh = r - jj * Gc;
+    if (r >= MT || jj >= ntok || hh >= nheads) return;
+    const int head = (kvh * G + g0 + hh) * gm.maps + mp;
+    constexpr int REC = VD + 2;
+    const float* src = part + (((size_t)blockIdx.x * gridDim.y + blockIdx.y) * MT + r) * gm.splits * REC;
+    const float sv = gm.sink ? (sink_values ? sink_values[head] : 0.f) * LOG2E : -INFINITY;
+    // ranges lane and lane + 32 (splits <= 64)
+    float mz[2], lz[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int z = lane + 32 * k;
+        mz[k] = z < gm.splits ? src[(size_t)z * REC + VD] : -INFINITY;
+        lz[k] = z < gm.splits ? src[(size_t)z * REC + VD + 1] : 0.f;
+    }
+    float M = fmaxf(sv, fmaxf(mz[0], mz[1]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float wz[2], L = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        wz[k] = mz[k] == -INFINITY ? 0.f : exp2f(mz[k] - M);
+        L += lz[k] * wz[k];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (gm.sink) L += exp2f(sv - M);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    TO* dst = out + (size_t)(q_begin + tok0 + jj) * out_stride + (size_t)head * VD;
+    constexpr int DPL = (VD + 31) / 32;                       // channels a lane
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+    for (int z = 0; z < gm.splits; ++z) {
+        const float w = __shfl_sync(0xffffffffu, wz[z >> 5], z & 31);
+        if (w == 0.f) continue;                               // an empty range: its sums were never written
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            if (d < VD) acc[i] = fmaf(src[(size_t)z * REC + d], w, acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= VD) continue;
+        if constexpr (sizeof(TO) == 4) dst[d] = acc[i] * inv; else dst[d] = __float2bfloat16(acc[i] * inv);
+    }
+}
+
 template <typename TO, bool VIK>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
            int table_stride, const int* cu_q, const int* kv_len, const int* tile_entry, const int* tile_tok0,
-           int n_tiles, const float* sink_values, const Geometry& gm, cudaStream_t s) {
+           int n_tiles, const float* sink_values, float* part, const Geometry& gm, cudaStream_t s) {
     static bool configured = false;
     const size_t smem = ((size_t)MT * KROW + 2 * ((size_t)KT * KROW + (VIK ? 0 : (size_t)KT * VROW))) * sizeof(bf16);
     if (!configured) {
@@ -314,10 +403,13 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* c
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(n_tiles, gm.Hkv * gm.maps * gm.chunks);
+    dim3 grid(n_tiles, gm.Hkv * gm.maps * gm.chunks, gm.splits);
     RI_CHECKED(ri_launch(attention_rows_kernel<TO, VIK>, grid, dim3(THREADS), smem, s, (const bf16*)q, q_stride, (TO*)out,
                          out_stride, (const bf16*)cache, block_table, table_stride, cu_q, kv_len, tile_entry, tile_tok0,
-                         sink_values, gm));
+                         sink_values, part, gm));
+    if (gm.splits > 1)
+        RI_CHECKED(ri_launch(attention_rows_merge_kernel<TO>, dim3(grid.x, grid.y, MT / MERGE_WARPS), dim3(MERGE_WARPS * 32), 0, s,
+                             (const float*)part, (TO*)out, out_stride, cu_q, tile_entry, tile_tok0, sink_values, gm));
     return ri_launch_status();
 }
 }  // namespace
@@ -341,20 +433,22 @@ RI_API int ri_attention_rows_tokens_per_tile(int Hq, int Hkv, int maps) {
 // q [T][q_stride] bf16, head h at column h*HD; out rows of out_stride, head h at column h*VD, fp32 (out_f32) or bf16.
 // cache: per page the keys [key head][slot][HD], then (unless value_in_key) the values [value head][slot][VD], bf16,
 // every page starting on a 16-byte boundary.  tile_entry[i]: batch entry of tile i (-1: skip), tile_tok0[i] its first
-// token within the entry; a tile holds ri_attention_rows_tokens_per_tile tokens.
+// token within the entry; a tile holds ri_attention_rows_tokens_per_tile tokens.  splits > 1: the key tiles of every CTA
+// in that many ranges through `part`, fp32 [n_tiles][key heads * chunks][64 rows][splits][VD + 2], and a second launch.
 RI_API int ri_attention_rows(const void* q, int q_stride, void* out, int out_stride, const void* cache,
                              const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                              const int* tile_entry, const int* tile_tok0, int n_tiles, int Hq, int Hkv, int page_size,
                              float scale, int window, int sink, float softcap, const float* sink_values, int maps,
-                             int value_in_key, int out_f32, void* stream) {
+                             int value_in_key, int out_f32, int splits, float* part, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
     const int gc = ri_attention_rows_heads_per_cta(Hq, Hkv, maps);
     if (gc <= 0 || (value_in_key && (maps != 1 || VD > HD)) || q_stride % 8) return (int)cudaErrorInvalidValue;
     const int G = Hq / (Hkv * maps);
-    Geometry gm{Hq, Hkv, maps, gc, (G + gc - 1) / gc, MT / gc, page_size, window, sink, scale, softcap};
+    Geometry gm{Hq, Hkv, maps, gc, (G + gc - 1) / gc, MT / gc, page_size, window, sink, splits, scale, softcap};
     cudaStream_t s = (cudaStream_t)stream;
 #define RI_ROWS_GO(TO, VIK) launch<TO, VIK>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q, kv_len, \
-                                            tile_entry, tile_tok0, n_tiles, sink_values, gm, s)
+                                            tile_entry, tile_tok0, n_tiles, sink_values, part, gm, s)
     if (value_in_key) {
         if constexpr (VD <= HD) return out_f32 ? RI_ROWS_GO(float, true) : RI_ROWS_GO(bf16, true);
         return (int)cudaErrorInvalidValue;

@@ -493,11 +493,14 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor, tile_tok0: torch.Tensor,
                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                    value_dim: Optional[int] = None, sink: bool = False, softcap: Optional[float] = None,
-                   sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
+                   sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False,
+                   splits: int = 1, part: Optional[torch.Tensor] = None) -> None:
     """`attention_plain` on the tensor cores for a bf16 cache: the scores are fp32 sums of products of bf16 q and
     k, cap, mask and softmax are fp32, and the softmax weights meet the bf16 values unrounded (three bf16 pieces a
-    weight).  Arguments as there, without `block`; tiles hold `attention_rows_tokens_per_tile` tokens."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0, sink_values)
+    weight).  Arguments as there, without `block`; tiles hold `attention_rows_tokens_per_tile` tokens.  `splits` > 1
+    cuts every tile's keys into that many ranges, a CTA each, joined by a second launch through `part` (fp32,
+    `attention_rows_scratch_floats` long): for few tiles over many keys."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0, sink_values, part)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_tok0, "tile_tok0")):
         _i32(t, n)
@@ -507,11 +510,23 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
     if out.dtype == torch.float32 and (out.stride(0) % 2 or out.data_ptr() % 8):
         raise KernelError("attention_rows: fp32 out rows start on 8-byte boundaries")
     page_size = _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key)
+    if splits > 1 and (part is None or part.dtype != torch.float32 or not part.is_contiguous() or part.data_ptr() % 16 or
+                       part.numel() < attention_rows_scratch_floats(tile_entry.numel(), num_heads, num_kv_heads, vd, maps, splits)):
+        raise KernelError("attention_rows: the scratch for the key ranges is too small")
     check(L.attention_rows(head_dim, vd).ri_attention_rows(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(cache), _p(block_table), block_table.stride(0), _p(cu_q),
         _p(kv_len), _p(tile_entry), _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads, page_size, float(scale),
         int(window) if window else 0, 1 if sink else 0, float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
-        1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()), "attention_rows")
+        1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, int(splits), _p(part) if splits > 1 else None,
+        stream_ptr()), "attention_rows", 2 if splits > 1 else 1)
+
+
+def attention_rows_scratch_floats(tiles: int, num_heads: int, num_kv_heads: int, value_dim: int, maps: int, splits: int) -> int:
+    """Elements of `attention_rows`' scratch: [tiles][key heads * CTAs a key head][64 rows][splits][value_dim + 2]."""
+    if splits <= 1:
+        return 0
+    group = num_heads // (num_kv_heads * maps)
+    return tiles * num_kv_heads * maps * (-(-group // min(group, 64))) * 64 * splits * (value_dim + 2)
 
 
 def attention_single_scratch_floats(entries: int, num_heads: int, value_dim: int, splits: int) -> int:

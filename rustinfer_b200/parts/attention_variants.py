@@ -27,12 +27,15 @@ from .spec import PartSpec
 
 class PlainAttend:
     """How a mixer sends its queries to the attention kernels with fp32 scores and softmax weights.  The bfloat16
-    engine: entries of one token go to the kernel that reads a key head once for all its query heads (where it
-    takes the geometry; the keys cut into ranges when few CTAs would walk many keys), everything else to the
-    tensor-core kernel in tiles of 64 (token, head) rows (where the sizes are multiples of 16), and what neither
-    takes to the fp32-arithmetic kernel in tiles of 16 query rows.  The 32-bit engine uses that last kernel alone,
-    whose sums do not depend on how the tokens were cut into steps."""
-    MAX_SPLITS = 16
+    engine: prompt portions go to the tensor-core kernel in tiles of 64 (token, head) rows (where the sizes are
+    multiples of 16).  Entries of one token go there too where eight or more query heads share a key head (one
+    cached row for all heads, say: the arithmetic of so many heads a key outgrows the fp32 pipes), else to the
+    kernel that reads a key head once for all its query heads (where it takes the geometry).  Both cut the keys
+    into ranges when few CTAs would walk many keys.  What neither takes runs on the fp32-arithmetic kernel in
+    tiles of 16 query rows.  The 32-bit engine uses that last kernel alone, whose sums do not depend on how the
+    tokens were cut into steps."""
+    MAX_SPLITS = 16             # of the one-CTA-a-key-head kernel
+    ROWS_MAX_SPLITS = 32        # of the tensor-core kernel
 
     def __init__(self, ctx: BuildContext, heads: int, kv_heads: int, head_dim: int, value_dim: int, maps: int = 1,
                  value_in_key: bool = False, window: Optional[int] = None):
@@ -40,28 +43,46 @@ class PlainAttend:
         self.Hq, self.Hkv, self.hd, self.vd, self.maps = heads, kv_heads, head_dim, value_dim, maps
         self.value_in_key, self.window = value_in_key, window
         fast = (ctx.dtype == torch.bfloat16 and os.environ.get("RUSTINFER_B200_BLOCK_ATTENTION", "fast") != "plain")
-        self.fast_single = fast and K.attention_single_supports(heads, kv_heads, head_dim, value_dim, maps)
         self.rows = fast and K.attention_rows_supports(head_dim, value_dim, value_in_key)
+        group = heads // (kv_heads * maps)
+        self.rows_single = self.rows and group >= 8
+        self.fast_single = (fast and not self.rows_single
+                            and K.attention_single_supports(heads, kv_heads, head_dim, value_dim, maps))
         rows = K.attention_rows_tokens_per_tile(heads, kv_heads, head_dim, value_dim, maps) if self.rows else 16
+        self._single = self.part = None
         if self.fast_single:
             self._single = single_token_entries()
-            self._tiles = token_tiles(rows, skip_single_token=True)
             key = ("single_scratch", heads, value_dim)
             if key not in ctx.shared:
                 n = K.attention_single_scratch_floats(ctx.max_batch_seqs, heads, value_dim, self.MAX_SPLITS)
                 ctx.shared[key] = torch.empty(n, dtype=torch.float32, device=ctx.device)
             self.part = ctx.shared[key]
-        else:
-            self._single = None
-            self._tiles = token_tiles(rows, skip_single_token=False)
+        elif self.rows_single:
+            self._single = single_token_entries()
+            self.ctas_per_tile = kv_heads * maps * -(-group // 64)
+            # ranges are made while tiles * CTAs a tile * ranges stays under 2 SMs' worth plus the tiles themselves
+            key = ("rows_scratch", value_dim)
+            if key not in ctx.shared:
+                ctx.shared[key] = torch.empty(4 * ctx.num_sms * 64 * (value_dim + 2), dtype=torch.float32, device=ctx.device)
+            self.part = ctx.shared[key]
+            if "zero_tok0" not in ctx.shared:
+                ctx.shared["zero_tok0"] = torch.zeros(ctx.max_batch_seqs + 4, dtype=torch.int32, device=ctx.device)
+            self.zero_tok0 = ctx.shared["zero_tok0"]
+        self._tiles = token_tiles(rows, skip_single_token=self._single is not None)
 
     def step_indices(self):
         return [self._tiles] if self._single is None else [self._single, self._tiles]
 
+    def _span(self, max_kv_len: int) -> int:
+        return min(max_kv_len, self.window) if self.window else max_kv_len
+
     def _splits(self, n_single: int, max_kv_len: int) -> int:
-        span = min(max_kv_len, self.window) if self.window else max_kv_len
         want = -(-4 * self.ctx.num_sms // max(1, n_single * self.Hkv * self.maps))
-        return max(1, min(want, -(-span // 128), self.MAX_SPLITS))
+        return max(1, min(want, -(-self._span(max_kv_len) // 128), self.MAX_SPLITS))
+
+    def _rows_splits(self, n_single: int, max_kv_len: int) -> int:
+        want = -(-2 * self.ctx.num_sms // max(1, n_single * self.ctas_per_tile))
+        return max(1, min(want, -(-self._span(max_kv_len) // 128), self.ROWS_MAX_SPLITS))
 
     def __call__(self, q: torch.Tensor, out: torch.Tensor, step: StepContext, cache: PagedLayerCache, scale: float,
                  softcap: Optional[float] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -70,10 +91,14 @@ class PlainAttend:
                     maps=self.maps, value_in_key=self.value_in_key)
         if self._single is not None:
             (single,) = step.index(self._single)
-            if single.numel():
+            if single.numel() and self.fast_single:
                 K.attention_single(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single, self.Hq, self.Hkv,
                                    self.hd, scale, self.window, None, splits=self._splits(single.numel(), step.max_kv_len),
                                    part=self.part, **opts)
+            elif single.numel():
+                K.attention_rows(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, single,
+                                 self.zero_tok0[: single.numel()], self.Hq, self.Hkv, self.hd, scale, self.window,
+                                 splits=self._rows_splits(single.numel(), step.max_kv_len), part=self.part, **opts)
         tile_entry, tile_tok0 = step.index(self._tiles)
         if tile_entry.numel():
             if self.rows:

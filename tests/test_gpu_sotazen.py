@@ -474,13 +474,14 @@ def test_two_map_attention_on_tensor_cores(dk, dv, H, G, window, cap):
         q[first:] = queries(targets).to(F64)
         return P.two_map_attention(q, keys[:T].to(F64), vals[:T].to(F64), 1.0, cap, window)[first:]
 
-    def attend(first, targets):
+    def attend(first, targets, splits=1):
         count = len(targets)
         out = torch.full((count, H * 2 * dv), float("nan"), dtype=torch.float32, device=DEV)
         tiles = list(range(0, count, tpt))
+        part = torch.full((K().attention_rows_scratch_floats(len(tiles), 2 * H, G, dv, 2, splits),), float("nan"), device=DEV)
         K().attention_rows(queries(targets).reshape(count, -1).to(BF).to(DEV), out, cache, bt, i32([0, count]),
                            i32([first + count]), i32([0] * len(tiles)), i32(tiles), 2 * H, G, d1, 1.0, window, dv,
-                           softcap=cap, maps=2)
+                           softcap=cap, maps=2, splits=splits, part=part)
         return out.cpu().view(count, H, 2, dv)
 
     w = window or 10 ** 9
@@ -496,7 +497,11 @@ def test_two_map_attention_on_tensor_cores(dk, dv, H, G, window, cap):
                     assert (lead < 1e-2) == (sh < w), (first, shift, m)
     for p, tgt in [(n - 1, 3), (n - 1, n - 1), (300, 0), (64, 63), (7, 0), (0, 0)]:
         tg = (tgt, min(p, tgt + 1))
-        assert float((attend(p, [tg])[0].to(F64) - plain_rows(p, [tg])[0]).abs().max()) < 2e-4, (p, tgt)
+        ref = plain_rows(p, [tg])[0]
+        for splits in (1, 2, 7):            # key ranges: some hold no visible key, some are empty
+            assert float((attend(p, [tg], splits)[0].to(F64) - ref).abs().max()) < 2e-4, (p, tgt, splits)
+    targets = [(max(0, p - 2), max(0, p - 40)) for p in range(250, 320)]
+    assert float((attend(250, targets, 3).to(F64) - plain_rows(250, targets)).abs().max()) < 2e-4
 
 
 @pytest.mark.parametrize("rank,r,H", [(32, 16, 4), (80, 16, 3), (64, 48, 20), (16, 16, 70), (256, 32, 8)])
@@ -533,13 +538,14 @@ def test_latent_rows_attention_on_tensor_cores(rank, r, H):
         p = P.softmax_rows(sc, P.visible(T, None), sink.to(F64))
         return torch.einsum("hij,jv->ihv", p, rows[:T, :rank].to(F64))[first:]
 
-    def attend(first, targets, dtype=torch.float32):
+    def attend(first, targets, dtype=torch.float32, splits=1):
         count = len(targets)
         out = torch.full((count, H * rank), float("nan"), dtype=dtype, device=DEV)
         tiles = list(range(0, count, tpt))
+        part = torch.full((K().attention_rows_scratch_floats(len(tiles), H, 1, rank, 1, splits),), float("nan"), device=DEV)
         K().attention_rows(queries(targets).reshape(count, -1).to(BF).to(DEV), out, cache, bt, i32([0, count]),
                            i32([first + count]), i32([0] * len(tiles)), i32(tiles), H, 1, kd, 0.5, None, rank,
-                           sink=True, sink_values=sink.to(DEV), value_in_key=True)
+                           sink=True, sink_values=sink.to(DEV), value_in_key=True, splits=splits, part=part)
         return out.float().cpu().view(count, H, rank)
 
     for first, count in ((45, 70), (0, 33)):
@@ -549,7 +555,12 @@ def test_latent_rows_attention_on_tensor_cores(rank, r, H):
             assert float((got.to(F64) - ref).abs().max()) < 2e-4, (first, shift)
     assert float((attend(45, list(range(45, 115)), BF).to(F64) - plain_rows(45, list(range(45, 115)))).abs().max()) < 1e-2
     for p, tgt in [(n - 1, 3), (n - 1, n - 1), (300, 0), (64, 63), (7, 0), (0, 0)]:
-        assert float((attend(p, [tgt])[0].to(F64) - plain_rows(p, [tgt])[0]).abs().max()) < 2e-4, (p, tgt)
+        ref = plain_rows(p, [tgt])[0]
+        for splits in (1, 2, 5, 16):        # key ranges joined by the second launch; the sink counts once
+            assert float((attend(p, [tgt], splits=splits)[0].to(F64) - ref).abs().max()) < 2e-4, (p, tgt, splits)
+    targets = [max(0, p - 100) for p in range(200, 270)]
+    assert float((attend(200, targets, splits=4).to(F64) - plain_rows(200, targets)).abs().max()) < 2e-4
+    assert float((attend(n - 1, [5], BF, splits=3)[0].to(F64) - plain_rows(n - 1, [5])[0]).abs().max()) < 1e-2
 
 
 # ============================================================================ the engine
