@@ -48,6 +48,9 @@ def _layer(mixer, ff=None):
 #    feed-forward (its `diff` small: with scores capped at 1.5 the two maps are nearly alike, and a weight near one on
 #    the second would leave a difference that is mostly rounding in bfloat16); a latent layer of three heads with a
 #    rotated part of four channels; alpha below one
+# D: every attention size a multiple of 16, so that the bfloat16 engine's prompt portions run on the tensor-core
+#    attention; a latent layer of eight heads, whose single tokens run there too with their keys in ranges once the
+#    context passes 128; attention with a window of 50 (three pages and two tokens) over two kv heads, whole maps rotated
 CONFIGS = {
     "A": {"architecture": "Sotazen", "width": 96, "vocab": 211, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.7},
           "postln_alpha": 2.0, "layers": [
@@ -64,6 +67,11 @@ CONFIGS = {
               _layer(_lightning(1, 20, 12, [0.95]), 72),
               _layer(_att(1, 1, 40, 8, 0.25, 0.15, mask=9, rot=(20, 1e6), softcap=1.5)),
               _layer(_latent(3, 20, 4, 36, 20, 0.35, 50.0), 80)]},
+    "D": {"architecture": "Sotazen", "width": 80, "vocab": 150, "norm": {"eps": 2e-5}, "embedding": {"scale": 1.5},
+          "postln_alpha": 1.5, "layers": [
+              _layer(_lightning(2, 16, 16, [0.7, 0.97]), 96),
+              _layer(_att(4, 2, 16, 32, 0.25, 0.4, mask=50, rot=(16, 20000.0), softcap=10.0), 112),
+              _layer(_latent(8, 16, 16, 24, 32, 0.2, 1000.0), 64)]},
 }
 
 

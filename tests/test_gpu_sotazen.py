@@ -715,7 +715,7 @@ def test_fp32_logits_do_not_depend_on_the_cut(models):
     assert rel_err(run_cuts(r, "t", ids, [60] + [1] * 30), whole) <= 2e-6
 
 
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "D"])
 def test_long_decoding_and_graphs(models, name):
     """300 single tokens after a short prompt, eager and from captured steps: windows pass, their pages are
     given back, the states carry, and the logits stay those of the plain model."""
