@@ -40,6 +40,7 @@ constexpr int KCH = HD / 8, VCH = VD / 8;      // 16-byte pieces a row
 constexpr int KS = HD / 16;                    // k-steps of q k^T
 constexpr int NT = VD / 8;                     // n-tiles of the output
 constexpr bool QREG = HD <= 128;               // the q fragments stay in registers
+constexpr int PVG = 4;                         // value fragments (16 channels each) a group of the weights' products
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -106,7 +107,7 @@ __device__ __forceinline__ void load_tile(bf16* Ks, bf16* Vs, const bf16* __rest
 }
 
 template <typename TO, bool VIK>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, VD <= 128 ? (VIK ? 4 : 3) : 1)      // values to 128 wide: three or four CTAs an SM
 attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__ out, int out_stride,
                       const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
                       const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -279,14 +280,24 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
                         c -= __uint_as_float(packed & 0xffff0000u);
                     }
                 }
+                // value fragments in groups of PVG: the products of one piece run over the whole group before the next
+                // piece adds to the same accumulators, so consecutive products do not wait for one another
 #pragma unroll
-                for (int np = 0; np < NT / 2; ++np) {
-                    unsigned vf[4];
-                    ldmatrix_x4_trans(vf, Vs + (kk * 16 + (lane & 15)) * VSTRIDE + np * 16 + (lane >> 4) * 8);
+                for (int np0 = 0; np0 < NT / 2; np0 += PVG) {
+                    unsigned vf[PVG][4];
+#pragma unroll
+                    for (int g = 0; g < PVG; ++g)
+                        if (np0 + g < NT / 2)
+                            ldmatrix_x4_trans(vf[g], Vs + (kk * 16 + (lane & 15)) * VSTRIDE + (np0 + g) * 16 + (lane >> 4) * 8);
 #pragma unroll
                     for (int piece = 2; piece >= 0; --piece) {
-                        mma_bf16(o[2 * np], pa[piece], vf[0], vf[1]);
-                        mma_bf16(o[2 * np + 1], pa[piece], vf[2], vf[3]);
+#pragma unroll
+                        for (int g = 0; g < PVG; ++g) {
+                            if (np0 + g < NT / 2) {
+                                mma_bf16(o[2 * (np0 + g)], pa[piece], vf[g][0], vf[g][1]);
+                                mma_bf16(o[2 * (np0 + g) + 1], pa[piece], vf[g][2], vf[g][3]);
+                            }
+                        }
                     }
                 }
             }
@@ -428,6 +439,24 @@ RI_API int ri_attention_rows_heads_per_cta(int Hq, int Hkv, int maps) {
 RI_API int ri_attention_rows_tokens_per_tile(int Hq, int Hkv, int maps) {
     const int gc = ri_attention_rows_heads_per_cta(Hq, Hkv, maps);
     return gc > 0 ? MT / gc : 0;
+}
+
+// CTAs of the attention kernel that fit an SM at once (0: the question failed), for the choice of the key ranges.
+RI_API int ri_attention_rows_ctas_per_sm(int value_in_key, int out_f32) {
+    int n = 0;
+    cudaError_t e = cudaErrorInvalidValue;
+#define RI_ROWS_OCC(TO, VIK) do { \
+        const size_t smem = ((size_t)MT * KROW + 2 * ((size_t)KT * KROW + (VIK ? 0 : (size_t)KT * VROW))) * sizeof(bf16); \
+        e = cudaFuncSetAttribute(attention_rows_kernel<TO, VIK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_rows_kernel<TO, VIK>, THREADS, smem); \
+    } while (0)
+    if (value_in_key) {
+        if constexpr (VD <= HD) { if (out_f32) RI_ROWS_OCC(float, true); else RI_ROWS_OCC(bf16, true); }
+    } else {
+        if (out_f32) RI_ROWS_OCC(float, false); else RI_ROWS_OCC(bf16, false);
+    }
+#undef RI_ROWS_OCC
+    return e == cudaSuccess ? n : 0;
 }
 
 // q [T][q_stride] bf16, head h at column h*HD; out rows of out_stride, head h at column h*VD, fp32 (out_f32) or bf16.

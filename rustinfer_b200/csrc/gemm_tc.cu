@@ -36,7 +36,9 @@ constexpr int BM = 128;                 // rows of the A operand per tile (MMA M
 constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
 constexpr int THREADS = 192;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3, EPI_ROPE = 4 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3, EPI_ROPE = 4, EPI_RELU2 = 5 };
+// EPI_RELU2: max(x, 0)^2 of the fp32 sum, stored bf16 (the activation of a feed-forward without a gate)
+__device__ __forceinline__ float relu2(float x) { return x > 0.f ? x * x : 0.f; }
 enum ErrorCode { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT = 2, ERR_EPILOGUE_WAIT = 3, ERR_DRAIN_WAIT = 4 };
 
 
@@ -127,6 +129,7 @@ __device__ __forceinline__ void store_one(const Params& p, int n_tok, int n_feat
     const size_t row = (size_t)tok * p.ld_out;
     switch (p.epilogue) {
         case EPI_BF16: reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(acc); break;
+        case EPI_RELU2: reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(relu2(acc)); break;
         case EPI_F32: reinterpret_cast<float*>(p.out)[row + feat] = acc; break;
         case EPI_RESIDUAL: atomicAdd(reinterpret_cast<float*>(p.out) + row + feat, acc); break;   // parts of one sum may come from several CTAs
         case EPI_SILU:                                   // even feature = gate_j, odd = up_j
@@ -151,6 +154,15 @@ __device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0,
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
             dst[0] = pack8(v);
             dst[1] = pack8(v + 8);
+            break;
+        }
+        case EPI_RELU2: {
+            float m[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m[j] = relu2(v[j]);
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
+            dst[0] = pack8(m);
+            dst[1] = pack8(m + 8);
             break;
         }
         case EPI_F32: {
@@ -191,6 +203,17 @@ __device__ __forceinline__ void store_row64(const Params& p, int tok, int feat0,
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[j] = pack8(v + 8 * j);
+            break;
+        }
+        case EPI_RELU2: {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float m[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) m[j] = relu2(v[8 * q + j]);
+                dst[q] = pack8(m);
+            }
             break;
         }
         case EPI_F32: {
@@ -978,7 +1001,7 @@ int gemm_tc_impl(const void* X, const void* W, int M, int N, int K, void* out, i
     p.tiles_a = (p.a_rows + BM - 1) / BM;
     const int tiles_b = (p.b_rows + bn - 1) / bn;
     p.n_tiles = p.tiles_a * tiles_b;
-    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU) ? 2 : 4;
+    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU || epilogue == EPI_RELU2) ? 2 : 4;
     p.vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((size_t)ld_out * esize) % 16 == 0) ? 1 : 0;
     CUtensorMap ma, mb;
     p.a_box = a_box;

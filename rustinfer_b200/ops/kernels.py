@@ -123,6 +123,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------------------ tcgen05 bf16 matrix product
 EPI_BF16, EPI_F32, EPI_SILU, EPI_RESIDUAL = 0, 1, 2, 3
+EPI_RELU2 = 5             # max(x, 0)^2 of the fp32 sums, stored bf16
 _tc_state = {}
 _TC_WORKSPACE_FLOATS = 8 << 20
 _TC_COUNTERS = 1 << 14
@@ -190,7 +191,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     """out = x[M,K] @ w[N,K]^T on the tcgen05 tensor cores, bf16 inputs, fp32 accumulation.
     epilogue: EPI_BF16 / EPI_F32 store into out [M,N]; EPI_SILU stores silu(gate)*up into
     out [M,N/2] for a weight whose rows alternate gate_j, up_j; EPI_RESIDUAL adds into the
-    fp32 out [M,N]."""
+    fp32 out [M,N]; EPI_RELU2 stores max(x, 0)^2 as bf16."""
     require_cuda(x, w, out)
     if not gemm_tc_supports(x, w):
         raise KernelError("gemm_tc: contiguous, 16-byte aligned bfloat16 x [M,K] and w [N,K] with K a multiple of 8")
@@ -199,7 +200,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     if w.shape[1] != Kd or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     cols = N // 2 if epilogue == EPI_SILU else N
-    want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU) else torch.float32
+    want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU, EPI_RELU2) else torch.float32
     if out.dtype != want or out.shape != (M, cols) or (epilogue == EPI_SILU and N % 2):
         raise KernelError(f"gemm_tc: out must be {want} [{M}, {cols}] for epilogue {epilogue}")
     plan = plan or gemm_tc_plan(M, N, Kd, num_sms, epilogue)
@@ -519,6 +520,13 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         int(window) if window else 0, 1 if sink else 0, float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
         1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, int(splits), _p(part) if splits > 1 else None,
         stream_ptr()), "attention_rows", 2 if splits > 1 else 1)
+
+
+def attention_rows_ctas_per_sm(head_dim: int, value_dim: int, value_in_key: bool, out_dtype: torch.dtype) -> int:
+    """CTAs of `attention_rows` that one SM holds at once, asked of the driver (at least 1)."""
+    n = L.attention_rows(head_dim, value_dim).ri_attention_rows_ctas_per_sm(1 if value_in_key else 0,
+                                                                             1 if out_dtype == torch.float32 else 0)
+    return max(1, int(n))
 
 
 def attention_rows_scratch_floats(tiles: int, num_heads: int, num_kv_heads: int, value_dim: int, maps: int, splits: int) -> int:

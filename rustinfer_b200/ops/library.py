@@ -47,6 +47,7 @@ _SIGNATURES = {
     "ri_attention_single_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _F, _P, _I, _I, _I, _P],
     "ri_attention_rows": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _F, _P, _I, _I, _I, _I, _P, _P],
     "ri_attention_rows_tokens_per_tile": [_I, _I, _I],
+    "ri_attention_rows_ctas_per_sm": [_I, _I],
     "ri_embed_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_round_rows": [_P, _P, _I, _L, _P],
     "ri_scale_add_norm": [_P, _P, _I, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],

@@ -60,10 +60,12 @@ class PlainAttend:
         elif self.rows_single:
             self._single = single_token_entries()
             self.ctas_per_tile = kv_heads * maps * -(-group // 64)
-            # ranges are made while tiles * CTAs a tile * ranges stays under 2 SMs' worth plus the tiles themselves
+            # ranges are made until the CTAs fill the SMs once: one CTA more than fit at once costs a second turn
+            self.slots = ctx.num_sms * K.attention_rows_ctas_per_sm(head_dim, value_dim, value_in_key,
+                                                                    torch.float32 if maps > 1 else ctx.dtype)
             key = ("rows_scratch", value_dim)
-            if key not in ctx.shared:
-                ctx.shared[key] = torch.empty(4 * ctx.num_sms * 64 * (value_dim + 2), dtype=torch.float32, device=ctx.device)
+            if key not in ctx.shared or ctx.shared[key].numel() < self.slots * 64 * (value_dim + 2):
+                ctx.shared[key] = torch.empty(self.slots * 64 * (value_dim + 2), dtype=torch.float32, device=ctx.device)
             self.part = ctx.shared[key]
             if "zero_tok0" not in ctx.shared:
                 ctx.shared["zero_tok0"] = torch.zeros(ctx.max_batch_seqs + 4, dtype=torch.int32, device=ctx.device)
@@ -81,8 +83,8 @@ class PlainAttend:
         return max(1, min(want, -(-self._span(max_kv_len) // 128), self.MAX_SPLITS))
 
     def _rows_splits(self, n_single: int, max_kv_len: int) -> int:
-        want = -(-2 * self.ctx.num_sms // max(1, n_single * self.ctas_per_tile))
-        return max(1, min(want, -(-self._span(max_kv_len) // 128), self.ROWS_MAX_SPLITS))
+        ctas = max(1, n_single * self.ctas_per_tile)
+        return max(1, min(self.slots // ctas, -(-self._span(max_kv_len) // 128), self.ROWS_MAX_SPLITS))
 
     def __call__(self, q: torch.Tensor, out: torch.Tensor, step: StepContext, cache: PagedLayerCache, scale: float,
                  softcap: Optional[float] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -68,7 +68,8 @@ class DenseMLP(FeedForward):
     """down( act(up(x)) ) without a gate.  params: hidden_size, intermediate_size, activation
     ("gelu": with erf; "gelu_tanh"; "tanh"; "relu_squared": max(z, 0)^2; "silu"), up_name / down_name (tensor names, default
     "up_proj.weight" / "down_proj.weight"), output ("float32": the result leaves the down projection in
-    32-bit).  The activation is computed in fp32."""
+    32-bit).  The activation is computed in fp32; the square of relu in the bfloat16 engine inside the
+    up product's epilogue, from the unrounded sums."""
 
     def __init__(self, params):
         super().__init__(params)
@@ -93,8 +94,10 @@ class DenseMLP(FeedForward):
         self.down = Linear(tensors[self.down_name], self.ctx.num_sms)
 
     def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
-        u = self.up(x, out_dtype=self.ctx.dtype)
-        K.activation(u, u, self.act)
+        u = self.up.relu_squared(x) if self.act == K.ACT_RELU_SQUARED and self.ctx.dtype == torch.bfloat16 else None
+        if u is None:                                     # other activations, the 32-bit engine, inputs the fused path refuses
+            u = self.up(x, out_dtype=self.ctx.dtype)
+            K.activation(u, u, self.act)
         if residual is not None and self.down.add_into(u, residual):
             return None
         return self.down(u, out_dtype=torch.float32 if self.out_fp32 else self.ctx.dtype)

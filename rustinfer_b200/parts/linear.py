@@ -58,6 +58,15 @@ class Linear:
         K.gemm_tc(x, self.weight, residual, K.EPI_RESIDUAL, num_sms=self.num_sms)
         return True
 
+    def relu_squared(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """max(x W^T, 0)^2 formed from the fp32 sums in the product's epilogue and stored bf16; None if
+        this weight cannot take that path."""
+        if not self._own(x):
+            return None
+        out = torch.empty((x.shape[0], self.out_features), dtype=torch.bfloat16, device=x.device)
+        K.gemm_tc(x, self.weight, out, K.EPI_RELU2, num_sms=self.num_sms)
+        return out
+
     def silu_pairs(self, x: torch.Tensor) -> Optional[torch.Tensor]:
         """For a weight whose rows alternate gate_j, up_j: silu(gate) * up, [M, out/2], fused
         into the product's epilogue; None if this weight cannot take that path."""

@@ -131,7 +131,7 @@ TC_SHAPES = [(1, 130, 96), (8, 3072, 2048), (17, 544, 96), (64, 391, 272), (65, 
              (2048, 2048, 72), (2048, 5120, 72), (1536, 2500, 72)]
 
 
-@pytest.mark.parametrize("epi", ["bf16", "f32", "silu", "residual"])
+@pytest.mark.parametrize("epi", ["bf16", "f32", "silu", "residual", "relu2"])
 @pytest.mark.parametrize("M,N,K_", TC_SHAPES)
 def test_gemm_tc_against_float64(M, N, K_, epi):
     """The tcgen05 kernel in both orientations (few tokens: weight on the 128-row side),
@@ -157,6 +157,10 @@ def test_gemm_tc_against_float64(M, N, K_, epi):
         out = torch.full((M, N), float("nan"), device=dev())
         k.gemm_tc(x, w, out, k.EPI_F32)
         close(out, ref, torch.float32)
+    elif epi == "relu2":
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        k.gemm_tc(x, w, out, k.EPI_RELU2)
+        close(out, ref.clamp_min(0.0) ** 2, torch.bfloat16)
     else:
         out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
         k.gemm_tc(x, w, out, k.EPI_BF16)
