@@ -463,35 +463,63 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ 
     }
 }
 
-// Joins the ranges of one (entry, head): M = the largest maximum (0 with the sink), L = sum l_z e^(m_z - M)
-// (+ e^(-M) for the sink), out = sum acc_z e^(m_z - M) / L.  Ranges in their order, so the sum is the same
-// whatever else runs.
+// Joins the ranges of one (entry, head), a warp each: M = the largest maximum (0 with the sink), L = sum
+// l_z e^(m_z - M) (+ e^(-M) for the sink), out = sum acc_z e^(m_z - M) / L.  Lane z holds range z's weight (ranges
+// beyond 32 in a second turn), so the ranges' numbers are loaded side by side rather than one after the other; the
+// sums run over the ranges in their order, so the result is the same whatever else runs.
 template <typename T>
-__global__ void attention_single_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
-                                              const int* __restrict__ cu_q, const int* __restrict__ entry_list,
-                                              int Hq, int splits, int sink, const float* __restrict__ sink_values) {
+__global__ void __launch_bounds__(32)
+attention_single_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int out_stride,
+                              const int* __restrict__ cu_q, const int* __restrict__ entry_list,
+                              int Hq, int splits, int sink, const float* __restrict__ sink_values) {
     pdl_trigger();
     pdl_wait();
     const int b = entry_list[blockIdx.y], h = blockIdx.x;
     if (b < 0) return;
     const int t = cu_q[b];
     if (cu_q[b + 1] - t != 1) return;
-    const float* src = part + ((size_t)blockIdx.y * Hq + h) * splits * (VD + 2);
-    const float sv = sink && sink_values ? sink_values[h] : 0.f;    // the sink's exponent
-    float M = sink ? sv : -INFINITY;
-    for (int z = 0; z < splits; ++z) M = fmaxf(M, src[(size_t)z * (VD + 2) + VD]);
-    float L = sink ? expf(sv - M) : 0.f;
-    for (int z = 0; z < splits; ++z) {
-        const float m = src[(size_t)z * (VD + 2) + VD];
-        if (m != -INFINITY) L += src[(size_t)z * (VD + 2) + VD + 1] * expf(m - M);
+    constexpr int REC = VD + 2;
+    const int lane = threadIdx.x;
+    const float* src = part + ((size_t)blockIdx.y * Hq + h) * splits * REC;
+    const float sv = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY;    // the sink's exponent
+    float mz[2], lz[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int z = lane + 32 * k;
+        mz[k] = z < splits ? src[(size_t)z * REC + VD] : -INFINITY;
+        lz[k] = z < splits ? src[(size_t)z * REC + VD + 1] : 0.f;
     }
-    for (int d = threadIdx.x; d < VD; d += blockDim.x) {
-        float acc = 0.f;
-        for (int z = 0; z < splits; ++z) {
-            const float m = src[(size_t)z * (VD + 2) + VD];
-            if (m != -INFINITY) acc = fmaf(src[(size_t)z * (VD + 2) + d], expf(m - M), acc);
+    float M = fmaxf(sv, fmaxf(mz[0], mz[1]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float wz[2], L = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        wz[k] = mz[k] == -INFINITY ? 0.f : expf(mz[k] - M);
+        L += lz[k] * wz[k];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (sink) L += expf(sv - M);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    constexpr int DPL = (VD + 31) / 32;                       // channels a lane
+    float acc[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int z = 0; z < splits; ++z) {
+        const float w = __shfl_sync(0xffffffffu, wz[z >> 5], z & 31);
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) {
+            const int d = lane + 32 * i;
+            // an empty range left its maximum at -inf and its sums unwritten: weight 0, and nothing read
+            if (d < VD && w != 0.f) acc[i] = fmaf(src[(size_t)z * REC + d], w, acc[i]);
         }
-        out[(size_t)t * out_stride + (size_t)h * VD + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < VD) out[(size_t)t * out_stride + (size_t)h * VD + d] = from_f32<T>(acc[i] * inv);
     }
 }
 
@@ -589,7 +617,7 @@ RI_API int ri_attention_single_ex(const void* q, int q_stride, void* out, int ou
     RI_CHECKED(ri_launch(attention_single_kernel<T, TO, GM>, dim3(grid), dim3(THREADS), smem, s, (const T*)q, q_stride, (TO*)out, \
         out_stride, (const T*)cache, block_table, table_stride, cu_q, kv_len, entry_list, Hq, Hkv, page_size, scale, \
         window, block, sink, part, ex)); \
-    if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<TO>, dim3(Hq, n_entries), dim3(VD < 64 ? 32 : 64), 0, s, \
+    if (splits > 1) RI_CHECKED(ri_launch(attention_single_merge_kernel<TO>, dim3(Hq, n_entries), dim3(32), 0, s, \
         (const float*)part, (TO*)out, out_stride, cu_q, entry_list, Hq, splits, sink, sink_values)); } while (0)
     if (dtype == RI_BF16 && out_f32) RI_SINGLE(bf16, float);
     else if (dtype == RI_BF16) RI_SINGLE(bf16, bf16);
