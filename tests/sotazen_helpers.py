@@ -50,7 +50,9 @@ def _layer(mixer, ff=None):
 #    rotated part of four channels; alpha below one
 # D: every attention size a multiple of 16, so that the bfloat16 engine's prompt portions run on the tensor-core
 #    attention; a latent layer of eight heads, whose single tokens run there too with their keys in ranges once the
-#    context passes 128; attention with a window of 50 (three pages and two tokens) over two kv heads, whole maps rotated
+#    context passes 128; attention with a window of 50 (three pages and two tokens) over two kv heads, whole maps rotated;
+#    a last attention layer of eight heads on one kv head without a window, whose single tokens take the same way
+#    with two maps
 CONFIGS = {
     "A": {"architecture": "Sotazen", "width": 96, "vocab": 211, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.7},
           "postln_alpha": 2.0, "layers": [
@@ -71,7 +73,8 @@ CONFIGS = {
           "postln_alpha": 1.5, "layers": [
               _layer(_lightning(2, 16, 16, [0.7, 0.97]), 96),
               _layer(_att(4, 2, 16, 32, 0.25, 0.4, mask=50, rot=(16, 20000.0), softcap=10.0), 112),
-              _layer(_latent(8, 16, 16, 24, 32, 0.2, 1000.0), 64)]},
+              _layer(_latent(8, 16, 16, 24, 32, 0.2, 1000.0), 64),
+              _layer(_att(8, 1, 16, 16, 0.3, 0.25, rot=(8, 700.0)))]},
 }
 
 
