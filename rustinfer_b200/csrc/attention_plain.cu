@@ -45,11 +45,14 @@ constexpr size_t SMEM_FLOATS = (size_t)QT * QS + (size_t)KC * KS + (size_t)KC * 
 //                    [kv head][map], and the maps of a head share the values of kv head = head / (heads / kv heads).
 //                    Hq counts query heads with their maps, Hkv the value heads; the cache holds Hkv * maps key heads.
 //   value_in_key     the value of a key is its own first VD channels; the cache holds keys only
+//   slopes           a linear distance bias: slopes[h] * (query position - key position) is taken off the score of
+//                    query head h, after scale and cap (null: none)
 struct Extra {
     float softcap;
     const float* sink_values;
     int maps;
     int value_in_key;
+    const float* slopes;
 };
 
 // key head and value head of query head h
@@ -107,6 +110,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ o
     // with a sink the sums start from a key of score 0 that has no value: maximum 0, sum exp(0 - 0) = 1
     // (with sink values: a term exp(sink_h) instead, so the maximum starts at sink_h)
     float m = sink ? (ex.sink_values ? ex.sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
+    const float slope = ex.slopes ? ex.slopes[h] : 0.f;
     float acc[NACC];
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.f;
@@ -152,6 +156,7 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ o
             const bool seen = row_valid && key <= p_row && key >= lo_row;
             float sc = dot * scale;
             if (ex.softcap > 0.f) sc = ex.softcap * tanhf(sc / ex.softcap);
+            if (ex.slopes) sc -= slope * (float)(p_row - key);
             s[c] = seen ? sc : -INFINITY;
             cmax = fmaxf(cmax, s[c]);
         }
@@ -246,6 +251,7 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ 
     const int t = cu_q[b];
     if (cu_q[b + 1] - t != 1) return;
     int p = kv_len[b] - 1;
+    const int p_query = p;                               // the token's own position (p becomes its range's end)
     int lo = window > 0 ? max(0, p - window + 1) : 0;
     if (block > 0) lo = max(lo, (p / block) * block);
     const int splits = gridDim.z;
@@ -332,8 +338,10 @@ attention_single_kernel(const T* __restrict__ q, int q_stride, TO* __restrict__ 
 #pragma unroll
             for (int g = 0; g < SG; ++g)
                 if (g < G) {
-                    const float x = s[g] * scale;
-                    sc[g * SK + kk] = ex.softcap > 0.f ? ex.softcap * tanhf(x / ex.softcap) : x;
+                    float x = s[g] * scale;
+                    if (ex.softcap > 0.f) x = ex.softcap * tanhf(x / ex.softcap);
+                    if (ex.slopes) x -= ex.slopes[head0 + g * head_step] * (float)(p_query - key);
+                    sc[g * SK + kk] = x;
                 }
         }
         __syncthreads();
@@ -563,9 +571,10 @@ RI_API int ri_attention_plain_ex(const void* q, int q_stride, void* out, int out
                                  const int* cu_q, const int* kv_len, const int* tile_entry,
                                  const int* tile_q0, int n_tiles, int Hq, int Hkv, int page_size,
                                  float scale, int window, int block, int sink, float softcap,
-                                 const float* sink_values, int maps, int value_in_key, int out_f32, void* stream) {
+                                 const float* sink_values, int maps, int value_in_key, int out_f32, const float* slopes,
+                                 void* stream) {
     if (n_tiles <= 0) return 0;
-    const Extra ex{softcap, sink_values, maps, value_in_key};
+    const Extra ex{softcap, sink_values, maps, value_in_key, slopes};
     if (!extra_fits(Hq, Hkv, ex)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RI_BF16 && out_f32)
@@ -585,7 +594,7 @@ RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_st
                               float scale, int window, int block, int sink, void* stream) {
     return ri_attention_plain_ex(q, q_stride, out, out_stride, cache, dtype, block_table, table_stride, cu_q, kv_len,
                                  tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, block, sink,
-                                 0.f, nullptr, 1, 0, 0, stream);
+                                 0.f, nullptr, 1, 0, 0, nullptr, stream);
 }
 
 // Entries that bring a single token (entry_list[i], -1: skip): keys and values of a kv head are read once
@@ -596,9 +605,10 @@ RI_API int ri_attention_single_ex(const void* q, int q_stride, void* out, int ou
                                   const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                                   const int* entry_list, int n_entries, int Hq, int Hkv, int page_size, float scale,
                                   int window, int block, int sink, int splits, float* part, float softcap,
-                                  const float* sink_values, int maps, int value_in_key, int out_f32, void* stream) {
+                                  const float* sink_values, int maps, int value_in_key, int out_f32,
+                                  const float* slopes, void* stream) {
     if (n_entries <= 0) return 0;
-    const Extra ex{softcap, sink_values, maps, value_in_key};
+    const Extra ex{softcap, sink_values, maps, value_in_key, slopes};
     if (!extra_fits(Hq, Hkv, ex)) return (int)cudaErrorInvalidValue;
     if (Hq / (Hkv * maps) > SG || SV > 4) return (int)cudaErrorNotSupported;
     if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
@@ -633,7 +643,7 @@ RI_API int ri_attention_single(const void* q, int q_stride, void* out, int out_s
                                int window, int block, int sink, int splits, float* part, void* stream) {
     return ri_attention_single_ex(q, q_stride, out, out_stride, cache, dtype, block_table, table_stride, cu_q, kv_len,
                                   entry_list, n_entries, Hq, Hkv, page_size, scale, window, block, sink, splits, part,
-                                  0.f, nullptr, 1, 0, 0, stream);
+                                  0.f, nullptr, 1, 0, 0, nullptr, stream);
 }
 
 RI_API int ri_attention_single_supports(int Hq, int Hkv) {

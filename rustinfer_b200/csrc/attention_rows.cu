@@ -82,6 +82,7 @@ struct Geometry {
     int sink;              // the denominator holds exp(sink_values[h]) (null: exp(0)) besides the keys' terms
     int splits;            // ranges the key tiles of a CTA are cut into (grid z); > 1: results go through `part`
     float scale, softcap;  // softcap 0: scores are not capped
+    const float* slopes;   // slopes[h] * (query position - key position) is taken off head h's scores (null: no such bias)
 };
 
 // keys k0 .. k0+KT-1 of key head `kh` (and, unless the values lie inside the keys, the values of value head `g`)
@@ -168,12 +169,13 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
     // this thread's two rows: 16 * warp + lane / 4 and that + 8
     int p_row[2], lo_row[2];
     bool ok_row[2];
-    float m[2], l[2] = {0.f, 0.f};
+    float m[2], l[2] = {0.f, 0.f}, slope[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         const int jj = r / Gc, hh = r - jj * Gc;
         ok_row[i] = jj < ntok && hh < nheads;
+        if (gm.slopes && ok_row[i]) slope[i] = gm.slopes[head_of(hh)];
         p_row[i] = p_first + jj;
         lo_row[i] = gm.window > 0 ? max(0, p_row[i] - gm.window + 1) : 0;
         m[i] = -INFINITY;
@@ -237,6 +239,7 @@ attention_rows_kernel(const bf16* __restrict__ q, int q_stride, TO* __restrict__
                     const int i = e >> 1;
                     float sc = s[n][e] * gm.scale;
                     if (gm.softcap > 0.f) sc = gm.softcap * tanhf(sc / gm.softcap);
+                    sc -= slope[i] * (float)(p_row[i] - key);
                     const bool seen = ok_row[i] && key <= p_row[i] && key >= lo_row[i];
                     s[n][e] = seen ? sc * LOG2E : -INFINITY;
                     mx[i] = fmaxf(mx[i], s[n][e]);
@@ -468,13 +471,14 @@ RI_API int ri_attention_rows(const void* q, int q_stride, void* out, int out_str
                              const int* block_table, int table_stride, const int* cu_q, const int* kv_len,
                              const int* tile_entry, const int* tile_tok0, int n_tiles, int Hq, int Hkv, int page_size,
                              float scale, int window, int sink, float softcap, const float* sink_values, int maps,
-                             int value_in_key, int out_f32, int splits, float* part, void* stream) {
+                             int value_in_key, int out_f32, int splits, float* part, const float* slopes,
+                             void* stream) {
     if (n_tiles <= 0) return 0;
     if (splits < 1 || splits > 64 || (splits > 1 && !part)) return (int)cudaErrorInvalidValue;
     const int gc = ri_attention_rows_heads_per_cta(Hq, Hkv, maps);
     if (gc <= 0 || (value_in_key && (maps != 1 || VD > HD)) || q_stride % 8) return (int)cudaErrorInvalidValue;
     const int G = Hq / (Hkv * maps);
-    Geometry gm{Hq, Hkv, maps, gc, (G + gc - 1) / gc, MT / gc, page_size, window, sink, splits, scale, softcap};
+    Geometry gm{Hq, Hkv, maps, gc, (G + gc - 1) / gc, MT / gc, page_size, window, sink, splits, scale, softcap, slopes};
     cudaStream_t s = (cudaStream_t)stream;
 #define RI_ROWS_GO(TO, VIK) launch<TO, VIK>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q, kv_len, \
                                             tile_entry, tile_tok0, n_tiles, sink_values, part, gm, s)

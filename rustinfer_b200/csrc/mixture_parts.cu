@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_route_kernel(const float* __restrict__ z, const TX* __restrict__ x, const float* __restrict__ router,
                  int d, const float* __restrict__ correction, int T, int E,
                  int top, int n_groups, int keep, int renorm, int* __restrict__ ids,
-                 float* __restrict__ weights, int* __restrict__ counts) {
+                 float* __restrict__ weights, int* __restrict__ counts, int score) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
@@ -69,7 +69,9 @@ moe_route_kernel(const float* __restrict__ z, const TX* __restrict__ x, const fl
     }
     if (warp != 0) return;                                 // the choice is one warp's work
     for (int e = lane; e < E; e += 32) {
-        const float sc = 1.0f / (1.0f + expf(-(x ? s[e] : z[(size_t)t * E + e])));
+        // score 0: the sigmoid of the logit; 1: the logit itself, the chosen ones' weights their softmax
+        const float zl = x ? s[e] : z[(size_t)t * E + e];
+        const float sc = score == 1 ? zl : 1.0f / (1.0f + expf(-zl));
         s[e] = sc;
         c[e] = sc + (correction ? correction[e] : 0.f);
     }
@@ -101,7 +103,7 @@ moe_route_kernel(const float* __restrict__ z, const TX* __restrict__ x, const fl
             if (gs[e / per] != INFINITY) c[e] = -INFINITY;
         __syncwarp();
     }
-    float wsum = 0.f;
+    float wsum = 0.f, zmax = 0.f;
     for (int r = 0; r < top; ++r) {
         float best = -INFINITY;
         int bi = 0x7fffffff;
@@ -117,10 +119,19 @@ moe_route_kernel(const float* __restrict__ z, const TX* __restrict__ x, const fl
             atomicAdd(counts + bi, 1);
             c[bi] = NAN;                                   // taken
         }
-        wsum += s[bi];
+        if (score == 1) {
+            if (r == 0) zmax = s[bi];                      // the first choice has the largest logit
+            wsum += expf(s[bi] - zmax);
+        } else {
+            wsum += s[bi];
+        }
         __syncwarp();
     }
-    if (renorm && lane < top) weights[(size_t)t * top + lane] /= wsum;
+    if (score == 1) {
+        if (lane < top) weights[(size_t)t * top + lane] = expf(weights[(size_t)t * top + lane] - zmax) / wsum;
+    } else if (renorm && lane < top) {
+        weights[(size_t)t * top + lane] /= wsum;
+    }
 }
 
 // --------------------------------------------------------------------------------- sort
@@ -179,11 +190,28 @@ __global__ void moe_sort_kernel(const int* __restrict__ ids, const int* __restri
 // ceil(rows / BM) + E tiles (no expert's count is known to the host) and a CTA beyond the last tile returns.
 constexpr int GBN = 64, GBK = 32;
 
+// What a gated pair (gate g, up u) becomes.  kind 0: silu(g) * u.  kind 1: with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit): g' * sigmoid(alpha * g') * (u' + 1).
+struct GluAct {
+    int kind;
+    float limit, alpha;
+};
+template <bool FAST>
+__device__ __forceinline__ float glu_pair(float g, float u, const GluAct& act) {
+    if (act.kind == 1) {
+        g = fminf(g, act.limit);
+        u = fminf(fmaxf(u, -act.limit), act.limit);
+        const float e = FAST ? __expf(-act.alpha * g) : expf(-act.alpha * g);
+        return g / (1.0f + e) * (u + 1.0f);
+    }
+    return g / (1.0f + (FAST ? __expf(-g) : expf(-g))) * u;
+}
+
 template <typename TA, typename TW, typename TO, int BM, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict__ w, TO* __restrict__ out,
                    int out_stride, const int* __restrict__ offsets, const int* __restrict__ order, int top,
-                   int gather, int E, int N, int K) {
+                   int gather, int E, int N, int K, GluAct act) {
     pdl_trigger();
     pdl_wait();
     constexpr int RM = BM / 16;                            // rows a thread: 16 thread rows
@@ -257,7 +285,7 @@ moe_product_kernel(const TA* __restrict__ a, int a_stride, const TW* __restrict_
             float v = acc[i][j];
             if (GATED) {
                 if (j & 1) continue;                                   // the pair's gate writes
-                v = v / (1.0f + expf(-v)) * acc[i][j + 1];
+                v = glu_pair<false>(v, acc[i][j + 1], act);
                 out[(size_t)(row0 + r) * out_stride + (n >> 1)] = from_f32<TO>(v);
             } else {
                 out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v);
@@ -299,7 +327,7 @@ template <typename TO, int BM, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __restrict__ w, TO* __restrict__ out,
                        int out_stride, const int* __restrict__ offsets, const int* __restrict__ order, int top,
-                       int gather, int E, int N, int K) {
+                       int gather, int E, int N, int K, GluAct act) {
     pdl_trigger();
     pdl_wait();
     constexpr int MB = BM / 16;                            // 16-row blocks
@@ -390,12 +418,25 @@ moe_product_mma_kernel(const bf16* __restrict__ a, int a_stride, const bf16* __r
                 const int n = n0 + warp * 16 + j * 8 + (lane & 3) * 2;
                 const float v0 = acc[m][j][2 * half], v1 = acc[m][j][2 * half + 1];
                 if (GATED) {
-                    if (n + 1 < Ntot) out[(size_t)(row0 + r) * out_stride + (n >> 1)] = from_f32<TO>(v0 / (1.0f + __expf(-v0)) * v1);
+                    if (n + 1 < Ntot) out[(size_t)(row0 + r) * out_stride + (n >> 1)] = from_f32<TO>(glu_pair<true>(v0, v1, act));
                 } else {
                     if (n < Ntot) out[(size_t)(row0 + r) * out_stride + n] = from_f32<TO>(v0);
                     if (n + 1 < Ntot) out[(size_t)(row0 + r) * out_stride + n + 1] = from_f32<TO>(v1);
                 }
             }
+}
+
+// --------------------------------------------------------------------- gated pairs, alone
+// in fp32 [rows][2 F], a row's columns alternating gate_n, up_n (what a product with a plain epilogue leaves):
+// out[p][n] = glu_pair(in[p][2n], in[p][2n + 1]).
+template <typename TO>
+__global__ void glu_pairs_kernel(const float* __restrict__ in, TO* __restrict__ out, long long total, GluAct act) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const float2 p = reinterpret_cast<const float2*>(in)[i];
+        out[i] = from_f32<TO>(glu_pair<false>(p.x, p.y, act));
+    }
 }
 
 // ------------------------------------------------------------------------------- gather
@@ -438,8 +479,9 @@ __global__ void moe_combine_kernel(const float* __restrict__ Y, const int* __res
 // Either z (fp32 [T][E]) or x ([T][d] of x_dtype) with router (fp32 [E][d]) is given.
 RI_API int ri_moe_route(const float* z, const void* x, int x_dtype, const float* router, int d, const float* correction,
                         int T, int E, int top, int n_groups, int keep,
-                        int renorm, int* ids, float* weights, int* counts, void* stream) {
+                        int renorm, int* ids, float* weights, int* counts, int score, void* stream) {
     if (T <= 0) return 0;
+    if (score != 0 && score != 1) return (int)cudaErrorInvalidValue;
     if (E <= 0 || top <= 0 || top > E || top > 32 || (n_groups > 0 && (E % n_groups || keep <= 0 || keep > n_groups)))
         return (int)cudaErrorInvalidValue;
     const int warps = ROUTE_WARPS;
@@ -449,10 +491,10 @@ RI_API int ri_moe_route(const float* z, const void* x, int x_dtype, const float*
     const dim3 grid(T);
     if (x && x_dtype == RI_BF16)
         RI_CHECKED(ri_launch(moe_route_kernel<bf16>, grid, dim3(32 * warps), smem, (cudaStream_t)stream, z, (const bf16*)x, router, d,
-                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
+                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts, score));
     else
         RI_CHECKED(ri_launch(moe_route_kernel<float>, grid, dim3(32 * warps), smem, (cudaStream_t)stream, z, (const float*)x, router, d,
-                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts));
+                             correction, T, E, top, n_groups > 0 ? n_groups : 0, keep, renorm, ids, weights, counts, score));
     return ri_launch_status();
 }
 
@@ -471,16 +513,19 @@ static int& ri_moe_tensor_cores() {
 }
 RI_API void ri_moe_set_tensor_cores(int on) { ri_moe_tensor_cores() = on ? 1 : 0; }
 
-// a_dtype / w_dtype / out_dtype: RI_F32 or RI_BF16.  rows: T * top (the pairs).  gated: see the kernel.
+// a_dtype / w_dtype / out_dtype: RI_F32 or RI_BF16.  rows: T * top (the pairs).  gated: see the kernel;
+// act_kind, act_limit, act_alpha: what a gated pair becomes (see GluAct).
 RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* w, int w_dtype, void* out, int out_dtype,
                           int out_stride, const int* offsets, const int* order, int top, int gather, int rows, int E,
-                          int N, int K, int gated, void* stream) {
+                          int N, int K, int gated, int act_kind, float act_limit, float act_alpha, void* stream) {
     if (rows <= 0) return 0;
+    if (act_kind != 0 && act_kind != 1) return (int)cudaErrorInvalidValue;
+    const GluAct act{act_kind, act_limit, act_alpha};
     cudaStream_t s = (cudaStream_t)stream;
     const int bm = ri_moe_product_rows(rows, E);
     const dim3 grid((rows + bm - 1) / bm + E, ((gated ? 2 * N : N) + GBN - 1) / GBN);
 #define RI_MP(TA, TW, TO, BM, G) RI_CHECKED(ri_launch(moe_product_kernel<TA, TW, TO, BM, G>, grid, dim3(256), 0, s, (const TA*)a, \
-        a_stride, (const TW*)w, (TO*)out, out_stride, offsets, order, top, gather, E, N, K))
+        a_stride, (const TW*)w, (TO*)out, out_stride, offsets, order, top, gather, E, N, K, act))
 #define RI_MP_BM(TA, TW, TO, G) do { if (bm == 64) RI_MP(TA, TW, TO, 64, G); else RI_MP(TA, TW, TO, 16, G); } while (0)
     const bool tensor_cores = a_dtype == RI_BF16 && w_dtype == RI_BF16 && K % 8 == 0 && a_stride % 8 == 0 &&
                               ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ri_moe_tensor_cores();
@@ -493,7 +538,7 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
             if (ce != cudaSuccess) return (int)ce; \
             configured = true; } \
         RI_CHECKED(ri_launch(moe_product_mma_kernel<TO, BM, G>, grid, dim3(128), smem, s, (const bf16*)a, a_stride, (const bf16*)w, \
-            (TO*)out, out_stride, offsets, order, top, gather, E, N, K)); } while (0)
+            (TO*)out, out_stride, offsets, order, top, gather, E, N, K, act)); } while (0)
         if (gated) { if (bm == 64) RI_MM(bf16, 64, true); else RI_MM(bf16, 16, true); }
         else { if (bm == 64) RI_MM(float, 64, false); else RI_MM(float, 16, false); }
 #undef RI_MM
@@ -506,6 +551,21 @@ RI_API int ri_moe_product(const void* a, int a_dtype, int a_stride, const void* 
     else return (int)cudaErrorInvalidValue;
 #undef RI_MP_BM
 #undef RI_MP
+    return ri_launch_status();
+}
+
+// in fp32 [rows][2 F] (8-byte aligned), out [rows][F] of out_dtype
+RI_API int ri_glu_pairs(const float* in, void* out, int out_dtype, long long total, int act_kind, float act_limit,
+                        float act_alpha, void* stream) {
+    if (total <= 0) return 0;
+    if ((act_kind != 0 && act_kind != 1) || ((uintptr_t)in & 7)) return (int)cudaErrorInvalidValue;
+    const GluAct act{act_kind, act_limit, act_alpha};
+    const long long nb = (total + 255) / 256;
+    const int blocks = (int)(nb < 8192 ? nb : 8192);
+    if (out_dtype == RI_BF16)
+        RI_CHECKED(ri_launch(glu_pairs_kernel<bf16>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, in, (bf16*)out, total, act));
+    else
+        RI_CHECKED(ri_launch(glu_pairs_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, in, (float*)out, total, act));
     return ri_launch_status();
 }
 

@@ -127,7 +127,8 @@ __global__ void latent_prepare_kernel(const TI* __restrict__ proj, int row_strid
                                       const int* __restrict__ positions, const float* __restrict__ cos_t,
                                       const float* __restrict__ sin_t, const int* __restrict__ slot_of_token,
                                       TA* __restrict__ cache, TA* __restrict__ q_plain, TA* __restrict__ q_full,
-                                      int H, int d, int r, int rank) {
+                                      int H, int d, int r, int rank, const TI* __restrict__ low_base, int low_stride,
+                                      int interleaved) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[33];
@@ -144,12 +145,15 @@ __global__ void latent_prepare_kernel(const TI* __restrict__ proj, int row_strid
     for (int e = tid; e < H * half; e += nth) {
         const int hh = e / half, i = e - hh * half;
         const TI* x = row + (size_t)hh * (d + r) + d;
-        const float u = to_f32<TI>(x[2 * i]), v = to_f32<TI>(x[2 * i + 1]), c = cr[i], s = sr[i];
+        // the pair that turns together: channels (2i, 2i+1), or (i, i + r/2)
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_f32<TI>(x[ia]), v = to_f32<TI>(x[ib]), c = cr[i], s = sr[i];
         TA* o = q_full + ((size_t)t * H + hh) * (rank + r) + rank;
-        o[2 * i] = from_f32<TA>(u * c - v * s);
-        o[2 * i + 1] = from_f32<TA>(v * c + u * s);
+        o[ia] = from_f32<TA>(u * c - v * s);
+        o[ib] = from_f32<TA>(v * c + u * s);
     }
-    const TI* low = row + (size_t)H * (d + r);
+    // the low-rank vector and the shared key part: behind the queries in the same row, or rows of their own
+    const TI* low = low_base ? low_base + (size_t)t * low_stride : row + (size_t)H * (d + r);
     float ss = 0.f;
     for (int i = tid; i < rank; i += nth) {
         const float v = to_f32<TI>(low[i]);
@@ -163,9 +167,10 @@ __global__ void latent_prepare_kernel(const TI* __restrict__ proj, int row_strid
     const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
     for (int i = tid; i < rank; i += nth) dst[i] = from_f32<TA>(to_f32<TI>(low[i]) * inv * wv(c_w, i));
     for (int i = tid; i < half; i += nth) {
-        const float u = to_f32<TI>(low[rank + 2 * i]), v = to_f32<TI>(low[rank + 2 * i + 1]), c = cr[i], s = sr[i];
-        dst[rank + 2 * i] = from_f32<TA>(u * c - v * s);
-        dst[rank + 2 * i + 1] = from_f32<TA>(v * c + u * s);
+        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_f32<TI>(low[rank + ia]), v = to_f32<TI>(low[rank + ib]), c = cr[i], s = sr[i];
+        dst[rank + ia] = from_f32<TA>(u * c - v * s);
+        dst[rank + ib] = from_f32<TA>(v * c + u * s);
     }
 }
 
@@ -257,17 +262,20 @@ RI_API int ri_diff_combine(const float* a, float lambda, float out_scale, float 
     return ri_launch_status();
 }
 
-// in_dtype: of proj; act_dtype: of q_plain, q_full and the cache; w_dtype: of the low-rank vector's norm weight.
+// in_dtype: of proj (and low); act_dtype: of q_plain, q_full and the cache; w_dtype: of the low-rank vector's norm weight.
+// low (may be null): rows [rank + r] of `low_stride` elements that hold the low-rank vector and the shared key part
+// where they do not follow the queries in proj's rows.  interleaved: rotary pairs (2i, 2i+1), else (i, i + r/2).
 // The cache of one layer is [pages][page][rank + r]: a token's row lies at slot_of_token[t] * (rank + r).
 RI_API int ri_latent_prepare(const void* proj, int in_dtype, int row_stride, const void* c_w, int w_dtype, float eps,
                              const int* positions, const float* cos_t, const float* sin_t, const int* slot_of_token,
                              void* cache, void* q_plain, void* q_full, int act_dtype, int tokens, int H, int d, int r,
-                             int rank, void* stream) {
+                             int rank, const void* low, int low_stride, int interleaved, void* stream) {
     if (tokens <= 0) return 0;
     if (r < 0 || (r & 1) || (r > 0 && (!cos_t || !sin_t || !positions))) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
 #define RI_LP(TI, TW, TA) RI_CHECKED(ri_launch(latent_prepare_kernel<TI, TW, TA>, dim3(tokens), dim3(256), 0, s, (const TI*)proj, \
-        row_stride, (const TW*)c_w, eps, positions, cos_t, sin_t, slot_of_token, (TA*)cache, (TA*)q_plain, (TA*)q_full, H, d, r, rank))
+        row_stride, (const TW*)c_w, eps, positions, cos_t, sin_t, slot_of_token, (TA*)cache, (TA*)q_plain, (TA*)q_full, H, d, r, rank, \
+        (const TI*)low, low_stride, interleaved))
     if (act_dtype == RI_BF16) {
         if (in_dtype == RI_BF16) { if (w_dtype == RI_BF16) RI_LP(bf16, bf16, bf16); else RI_LP(bf16, float, bf16); }
         else { if (w_dtype == RI_BF16) RI_LP(float, bf16, bf16); else RI_LP(float, float, bf16); }

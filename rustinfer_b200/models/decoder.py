@@ -9,8 +9,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts import (attention, attention_variants, experts, ffn, hyper, linear_attention, norm, parallel, rope,  # noqa: F401
-                     stem_tail)  # (registers the built-in parts)
+from ..parts import (attention, attention_variants, experts, ffn, hyper, linear_attention, norm, parallel,  # noqa: F401
+                     recurrent_unit, rope, short_conv, stem_tail)  # (registers the built-in parts)
 from ..parts.base import EMBEDDINGS, HEADS, NORMS, BuildContext, CacheNeed, ParamDecl, StepContext, StepIndex
 from ..parts.block import Block, Hidden
 from ..parts.spec import ModelSpec
@@ -111,6 +111,14 @@ class Decoder:
             h = torch.empty((s.streams, step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
             self.embed.forward(step, h[0])
             hidden = Hidden(h, None, fresh=True)
+        elif s.depth_average:
+            # every run entry's result is kept beside the stem's output; the layers hand on averages of them
+            hist = torch.empty((len(s.run_order) + 1, step.num_tokens, s.hidden_size), dtype=torch.float32,
+                               device=self.ctx.device)
+            self.embed.forward(step, hist[0])
+            hidden = Hidden(hist[0], None, history=hist, depth=1,
+                            average=torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32,
+                                                device=self.ctx.device))
         else:
             h = torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
             self.embed.forward(step, h)

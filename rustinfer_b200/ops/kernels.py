@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 import ctypes
-from typing import Dict, Optional, Sequence
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -397,7 +397,8 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                     tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: Optional[int], block: Optional[int] = None,
                     value_dim: Optional[int] = None, sink: bool = False, softcap: Optional[float] = None,
-                    sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
+                    sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False,
+                    slopes: Optional[torch.Tensor] = None) -> None:
     """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*vd].  `block`: a query
     sees only the keys of its own block of that many positions (counted from 0).  `value_dim`:
     size of a value where it is not the keys'; the cache is then [pages, Hkv*page*(hd+vd)].  `sink`:
@@ -406,9 +407,11 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
     `maps` m: every head has m attention maps with queries and keys of their own over one set of
     values; `num_heads` counts query heads with their maps ([head][map]), `num_kv_heads` the value
     heads, and the cache holds Hkv*m key heads ([kv head][map]).  `value_in_key`: a key's value is
-    its own first `value_dim` channels, and the cache holds keys only.  `out` may be fp32 whatever
-    the cache's dtype."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0, sink_values)
+    its own first `value_dim` channels, and the cache holds keys only.  `slopes` (fp32 [Hq]): a linear
+    distance bias, slopes[h] * (query position - key position) taken off head h's scores after scale
+    and cap.  `out` may be fp32 whatever the cache's dtype."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0, sink_values, slopes)
+    _slopes_ok(slopes, num_heads)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_q0, "tile_q0")):
         _i32(t, n)
@@ -421,8 +424,14 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                                     num_heads, num_kv_heads, page_size, float(scale),
                                     int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
                                     float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
-                                    1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()),
+                                    1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, _p(slopes),
+                                    stream_ptr()),
           "attention_plain")
+
+
+def _slopes_ok(slopes: Optional[torch.Tensor], num_heads: int) -> None:
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != num_heads or not slopes.is_contiguous()):
+        raise KernelError("attention: slopes is fp32 [heads]")
 
 
 def _attention_common(q, out, cache, num_heads, num_kv_heads, head_dim, vd, sink_values, maps, value_in_key) -> int:
@@ -452,12 +461,14 @@ def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                      block: Optional[int] = None, value_dim: Optional[int] = None, sink: bool = False,
                      splits: int = 1, part: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
-                     sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False) -> None:
+                     sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False,
+                     slopes: Optional[torch.Tensor] = None) -> None:
     """Attention of the entries that bring one token (`entry_list`, int32; -1 skips): fp32 arithmetic, a kv
     head's keys and values read once for all its query heads.  Arguments as `attention_plain`.  `splits` > 1
     cuts every entry's keys into that many ranges, a CTA each, joined by a second launch through `part`
     (fp32, `attention_single_scratch_floats` long)."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list, part, sink_values)
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, entry_list, part, sink_values, slopes)
+    _slopes_ok(slopes, num_heads)
     if splits > 1 and (part is None or part.dtype != torch.float32 or not part.is_contiguous() or
                        part.numel() < attention_single_scratch_floats(entry_list.numel(), num_heads, value_dim or head_dim, splits)):
         raise KernelError("attention_single: the scratch for the key ranges is too small")
@@ -472,7 +483,8 @@ def attention_single(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bl
                                      int(window) if window else 0, int(block) if block else 0, 1 if sink else 0,
                                      int(splits), _p(part) if splits > 1 else None,
                                      float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
-                                     1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, stream_ptr()),
+                                     1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, _p(slopes),
+                                     stream_ptr()),
           "attention_single", 2 if splits > 1 else 1)
 
 
@@ -495,13 +507,14 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                    value_dim: Optional[int] = None, sink: bool = False, softcap: Optional[float] = None,
                    sink_values: Optional[torch.Tensor] = None, maps: int = 1, value_in_key: bool = False,
-                   splits: int = 1, part: Optional[torch.Tensor] = None) -> None:
+                   splits: int = 1, part: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None) -> None:
     """`attention_plain` on the tensor cores for a bf16 cache: the scores are fp32 sums of products of bf16 q and
     k, cap, mask and softmax are fp32, and the softmax weights meet the bf16 values unrounded (three bf16 pieces a
     weight).  Arguments as there, without `block`; tiles hold `attention_rows_tokens_per_tile` tokens.  `splits` > 1
     cuts every tile's keys into that many ranges, a CTA each, joined by a second launch through `part` (fp32,
     `attention_rows_scratch_floats` long): for few tiles over many keys."""
-    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0, sink_values, part)
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0, sink_values, part, slopes)
+    _slopes_ok(slopes, num_heads)
     for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
                  (tile_entry, "tile_entry"), (tile_tok0, "tile_tok0")):
         _i32(t, n)
@@ -519,7 +532,7 @@ def attention_rows(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, bloc
         _p(kv_len), _p(tile_entry), _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads, page_size, float(scale),
         int(window) if window else 0, 1 if sink else 0, float(softcap) if softcap else 0.0, _p(sink_values), int(maps),
         1 if value_in_key else 0, 1 if out.dtype == torch.float32 else 0, int(splits), _p(part) if splits > 1 else None,
-        stream_ptr()), "attention_rows", 2 if splits > 1 else 1)
+        _p(slopes), stream_ptr()), "attention_rows", 2 if splits > 1 else 1)
 
 
 def attention_rows_ctas_per_sm(head_dim: int, value_dim: int, value_in_key: bool, out_dtype: torch.dtype) -> int:
@@ -555,6 +568,154 @@ def paged_cache_page_size(cache: torch.Tensor, num_kv_heads: int, head_dim: int,
     if cache.dim() != 2 or cache.shape[1] % per_token:
         raise KernelError("attention: cache must be [pages, page * (key heads * head_dim + value heads * value_dim)]")
     return cache.shape[1] // per_token
+
+
+# ------------------------------------- depth average, short convolutions, the gated linear recurrent unit
+def _f32_vec(t: Optional[torch.Tensor], n: int, name: str) -> None:
+    if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+        raise KernelError(f"{name} is contiguous fp32 [{n}]")
+
+
+def rms_sandwich(h_in: torch.Tensor, delta: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
+                 h_out: Optional[torch.Tensor], next_w: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float,
+                 rows: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None, n_prev: int = 0,
+                 dwa: Optional[torch.Tensor] = None, avg_out: Optional[torch.Tensor] = None) -> None:
+    """RMS norms around a sublayer and the weighted depth average, one launch; v is a row of h_in (fp32 [T, d],
+    rows may be a column view):
+        delta given:  v += rms(delta) * post_w;   h_out given: h_out <- v;
+        dwa given:    v <- sum_{j < n_prev} dwa[j] * history[j] + dwa[n_prev] * v;   avg_out given: avg_out <- v;
+        out given:    out <- rms(v) * next_w (None: 1)
+    with rms(x) = x / sqrt(mean(x^2) + eps).  Weights are fp32 (whatever a model adds to or multiplies into them is
+    the caller's business); history is fp32 [layers, T, d].  `rows` (int32): only those rows are read and only
+    `out` is written."""
+    require_cuda(h_in, delta, post_w, h_out, next_w, out, rows, history, dwa, avg_out)
+    _i32(rows, "rows")
+    T, d = h_in.shape
+    if h_in.dtype != torch.float32 or h_in.stride(1) != 1:
+        raise KernelError("rms_sandwich: h_in is fp32 [T, d] with unit column stride")
+    if delta is not None and (delta.shape != h_in.shape or delta.stride(1) != 1 or post_w is None):
+        raise KernelError("rms_sandwich: delta has h_in's shape and unit column stride, and comes with post_w")
+    _f32_vec(post_w, d, "rms_sandwich: post_w"); _f32_vec(next_w, d, "rms_sandwich: next_w")
+    for t, n in ((h_out, "h_out"), (avg_out, "avg_out")):
+        if t is not None and (t.dtype != torch.float32 or t.shape != h_in.shape or not t.is_contiguous()):
+            raise KernelError(f"rms_sandwich: {n} is contiguous fp32 [T, d]")
+    if dwa is not None:
+        _f32_vec(dwa, n_prev + 1, "rms_sandwich: dwa")
+        if n_prev and (history is None or history.dtype != torch.float32 or not history.is_contiguous()
+                       or history.dim() != 3 or history.shape[0] < n_prev or tuple(history.shape[1:]) != (T, d)):
+            raise KernelError("rms_sandwich: history is contiguous fp32 [>= n_prev, T, d]")
+    n_rows = T if rows is None else rows.numel()
+    if out is not None and (out.shape != (n_rows, d) or not out.is_contiguous()):
+        raise KernelError("rms_sandwich: out is contiguous [rows, d]")
+    check(L.core().ri_rms_sandwich(_p(h_in), h_in.stride(0), _p(delta), dtype_code(delta.dtype) if delta is not None else 0,
+                                   delta.stride(0) if delta is not None else 0, _p(post_w), _p(h_out), _p(history),
+                                   T * d, int(n_prev), _p(dwa), _p(avg_out), _p(next_w), _p(out),
+                                   dtype_code(out.dtype) if out is not None else 0, _p(rows), n_rows, d, float(eps),
+                                   stream_ptr()), "rms_sandwich")
+
+
+def short_conv_max_taps() -> int:
+    return int(L.core().ri_short_conv_max_taps())
+
+
+def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int, max_q_len: int,
+               residual: bool, in_bias: Optional[torch.Tensor] = None) -> None:
+    """A causal convolution over time on every channel, continued from a state: out[t] = (x[t] if residual) + bias +
+    sum_j weight[:, j] * x[t - taps + 1 + j] over each entry's tokens (x [T, C], may be a column view; weight fp32
+    [C, taps]); the taps - 1 inputs before an entry's first token come from state[slot] (fp32 [slots, taps - 1, C],
+    oldest first) and the entry's last taps - 1 inputs go back there.  `in_bias` (fp32 [C]) is added to every input
+    first (the state holds the sums)."""
+    require_cuda(x, weight, bias, state, cu_q, state_slots, out, in_bias)
+    _f32_vec(in_bias, x.shape[1], "short_conv: in_bias")
+    _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
+    T, C = x.shape
+    taps = weight.shape[1]
+    if x.stride(1) != 1 or out.shape != x.shape or out.stride(1) != 1:
+        raise KernelError("short_conv: x and out are [T, C] with unit column stride")
+    if weight.dtype != torch.float32 or weight.shape[0] != C or not weight.is_contiguous():
+        raise KernelError("short_conv: weight is contiguous fp32 [C, taps]")
+    _f32_vec(bias, C, "short_conv: bias")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (taps - 1, C):
+        raise KernelError("short_conv: state is contiguous fp32 [slots, taps - 1, C]")
+    check(L.core().ri_short_conv(_p(x), dtype_code(x.dtype), x.stride(0), _p(weight), _p(bias), _p(state), _p(cu_q),
+                                 _p(state_slots), _p(out), dtype_code(out.dtype), out.stride(0), int(n_entries),
+                                 int(max_q_len), C, taps, 1 if residual else 0, _p(in_bias), stream_ptr()), "short_conv")
+
+
+def rglru_gates(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor,
+                lam: torch.Tensor, decay_scale: float, a_out: torch.Tensor, x_out: torch.Tensor) -> None:
+    """Gates of the real-gated linear recurrent unit: u fp32 [T, C] in `blocks` equal parts, wa / wi [blocks, bs, bs]
+    ([out, in]), ba / bi / lam fp32 [C]:  r = sigmoid(wa u + ba), i = sigmoid(wi u + bi),
+    a_out = exp(-decay_scale * r * softplus(lam)),  x_out = sqrt(1 - a_out^2) * i * u.  fp32 throughout."""
+    require_cuda(u, wa, wi, ba, bi, lam, a_out, x_out)
+    T, C = u.shape
+    blocks = wa.shape[0]
+    if u.dtype != torch.float32 or u.stride(1) != 1:
+        raise KernelError("rglru_gates: u is fp32 [T, C] with unit column stride")
+    if blocks <= 0 or C % blocks or tuple(wa.shape) != (blocks, C // blocks, C // blocks) or wi.shape != wa.shape \
+            or wi.dtype != wa.dtype or not wa.is_contiguous() or not wi.is_contiguous():
+        raise KernelError("rglru_gates: wa and wi are contiguous [blocks, C / blocks, C / blocks] of one dtype")
+    for t, n in ((ba, "ba"), (bi, "bi"), (lam, "lam")):
+        _f32_vec(t, C, "rglru_gates: " + n)
+    for t in (a_out, x_out):
+        if t.dtype != torch.float32 or t.shape != (T, C) or not t.is_contiguous():
+            raise KernelError("rglru_gates: a_out and x_out are contiguous fp32 [T, C]")
+    check(L.core().ri_rglru_gates(_p(u), u.stride(0), _p(wa), _p(wi), dtype_code(wa.dtype), _p(ba), _p(bi), _p(lam),
+                                  float(decay_scale), _p(a_out), _p(x_out), T, C, blocks, stream_ptr()), "rglru_gates")
+
+
+def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int) -> None:
+    """S_t = a_t * S_(t-1) + x_t per channel over each entry's tokens, from state[slot] (fp32 [slots, C]) and back
+    into it; out[t] = S_t * gelu_tanh(y[t] + y_bias).  a, x fp32 [T, C]; y fp32 [T, C], may be a column view."""
+    require_cuda(a, x, y, y_bias, state, cu_q, state_slots, out)
+    _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
+    T, C = a.shape
+    for t in (a, x):
+        if t.dtype != torch.float32 or t.shape != (T, C) or not t.is_contiguous():
+            raise KernelError("rglru_scan: a and x are contiguous fp32 [T, C]")
+    if y.dtype != torch.float32 or y.shape != (T, C) or y.stride(1) != 1:
+        raise KernelError("rglru_scan: y is fp32 [T, C] with unit column stride")
+    _f32_vec(y_bias, C, "rglru_scan: y_bias")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (C,):
+        raise KernelError("rglru_scan: state is contiguous fp32 [slots, C]")
+    if out.shape != (T, C) or not out.is_contiguous():
+        raise KernelError("rglru_scan: out is contiguous [T, C]")
+    check(L.core().ri_rglru_scan(_p(a), _p(x), _p(y), y.stride(0), _p(y_bias), _p(state), _p(cu_q), _p(state_slots),
+                                 _p(out), dtype_code(out.dtype), int(n_entries), C, stream_ptr()), "rglru_scan")
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, group: int, out: torch.Tensor) -> None:
+    """out[t, j] = o[t, j] * sigmoid(gate[t, j // group]): o [T, n], gate fp32 [T, n / group] (both may be column
+    views).  group 1: a gate a channel; group = a head's width: a gate a head."""
+    require_cuda(o, gate, out)
+    T, n = o.shape
+    if o.stride(1) != 1 or gate.dtype != torch.float32 or gate.stride(1) != 1 or n % group or gate.shape != (T, n // group):
+        raise KernelError("sigmoid_gate: o [T, n], gate fp32 [T, n / group], unit column strides")
+    if out.shape != o.shape or not out.is_contiguous():
+        raise KernelError("sigmoid_gate: out is contiguous [T, n]")
+    check(L.core().ri_sigmoid_gate(_p(o), dtype_code(o.dtype), o.stride(0), _p(gate), gate.stride(0), int(group), _p(out),
+                                   dtype_code(out.dtype), T, n, stream_ptr()), "sigmoid_gate")
+
+
+def softcap(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap), fp32, in place."""
+    require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("softcap: x is contiguous fp32")
+    check(L.core().ri_softcap(_p(x), x.numel(), float(cap), stream_ptr()), "softcap")
+
+
+def glu_pairs(pairs: torch.Tensor, out: torch.Tensor, act: Optional[Tuple[float, float]] = None) -> None:
+    """pairs fp32 [rows, 2F], a row's columns alternating gate_n, up_n: out[p, n] = silu(gate) * up, or with `act`
+    (limit, alpha) g' sigmoid(alpha g') (u' + 1) with g' = min(gate, limit), u' = clamp(up, -limit, limit)."""
+    require_cuda(pairs, out)
+    _contig(pairs, "pairs"); _contig(out, "out")
+    if pairs.dtype != torch.float32 or pairs.shape[1] % 2 or out.shape != (pairs.shape[0], pairs.shape[1] // 2):
+        raise KernelError("glu_pairs: pairs fp32 [rows, 2F], out [rows, F]")
+    check(L.core().ri_glu_pairs(_p(pairs), _p(out), dtype_code(out.dtype), out.numel(), 1 if act else 0,
+                                float(act[0]) if act else 0.0, float(act[1]) if act else 0.0, stream_ptr()), "glu_pairs")
 
 
 # ------------------------------------------------ parts of decoders that are not the Llama shape
@@ -740,11 +901,14 @@ def qkv_prepare(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_weight: Optio
 # ------------------------------------------------------------------------ routed experts
 def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top: int, n_groups: int, keep: int, renorm: bool,
               ids: torch.Tensor, weights: torch.Tensor, counts: torch.Tensor, x: Optional[torch.Tensor] = None,
-              router: Optional[torch.Tensor] = None) -> None:
+              router: Optional[torch.Tensor] = None, score: str = "sigmoid") -> None:
     """The `top` experts of every token (ids int32 [T, top]) and their weights (fp32 [T, top]) from router logits:
     either z [T, E] fp32 is given, or x [T, d] and the router's matrix (fp32 [E, d]) and the kernel forms z = x W^T
     itself in fp32.  Scores sigmoid(z), chosen by score + correction among the experts of the `keep` best of
-    `n_groups` groups (0: no groups).  counts (int32 [E]) gets one added per choice."""
+    `n_groups` groups (0: no groups).  With `score` "softmax_chosen" the scores are the logits themselves and the
+    weights the softmax of the chosen logits among themselves.  counts (int32 [E]) gets one added per choice."""
+    if score not in ("sigmoid", "softmax_chosen"):
+        raise KernelError(f"moe_route: score {score!r}")
     require_cuda(z, correction, ids, weights, counts, x, router)
     E = counts.numel()
     T = ids.shape[0]
@@ -764,7 +928,7 @@ def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top
         raise KernelError("moe_route: correction fp32 [E], ids int32 and weights fp32 [T, top], counts [E]")
     check(L.core().ri_moe_route(_p(z), _p(x), dtype_code(x.dtype) if x is not None else 0, _p(router), d, _p(correction), T, E,
                                 int(top), int(n_groups), int(keep), 1 if renorm else 0, _p(ids), _p(weights), _p(counts),
-                                stream_ptr()), "moe_route")
+                                1 if score == "softmax_chosen" else 0, stream_ptr()), "moe_route")
 
 
 def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
@@ -780,10 +944,12 @@ def moe_sort(ids: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, ord
 
 
 def moe_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, order: Optional[torch.Tensor],
-                top: int, gated: bool) -> None:
+                top: int, gated: bool, act: Optional[Tuple[float, float]] = None) -> None:
     """Rows in expert order times their expert's matrix w [E, Ntot, K]: row p is a[order[p] // top] when `order`
     is given, else a[p].  gated: Ntot = 2N and the rows of w_e alternate gate_n, up_n: out[p][n] =
-    silu(a . w_e[2n]) * (a . w_e[2n+1]); else out[p] = a w_e^T.  fp32 sums in the order of k."""
+    silu(a . w_e[2n]) * (a . w_e[2n+1]); else out[p] = a w_e^T.  `act` (limit, alpha) with gated: the pair
+    (g, u) becomes g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit) instead.
+    fp32 sums in the order of k."""
     require_cuda(a, w, out, offsets, order)
     _contig(w, "w"); _i32(offsets, "offsets"); _i32(order, "order")
     E, Ntot, Kd = w.shape
@@ -794,7 +960,9 @@ def moe_product(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: to
         raise KernelError(f"moe_product: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
     check(L.core().ri_moe_product(_p(a), dtype_code(a.dtype), a.stride(0), _p(w), dtype_code(w.dtype), _p(out),
                                   dtype_code(out.dtype), out.stride(0), _p(offsets), _p(order), int(top),
-                                  1 if order is not None else 0, rows, E, N, Kd, 1 if gated else 0, stream_ptr()),
+                                  1 if order is not None else 0, rows, E, N, Kd, 1 if gated else 0,
+                                  1 if act else 0, float(act[0]) if act else 0.0, float(act[1]) if act else 0.0,
+                                  stream_ptr()),
           "moe_product")
 
 
@@ -1082,16 +1250,22 @@ def diff_combine(a: torch.Tensor, lam: float, out_scale: float, eps: float, gate
 def latent_prepare(proj: torch.Tensor, c_weight: torch.Tensor, eps: float, positions: torch.Tensor,
                    cos: torch.Tensor, sin: torch.Tensor, slot_of_token: Optional[torch.Tensor],
                    cache: Optional[torch.Tensor], q_plain: torch.Tensor, q_full: torch.Tensor, num_heads: int,
-                   head_dim: int, rot_dim: int, rank: int) -> None:
+                   head_dim: int, rot_dim: int, rank: int, low: Optional[torch.Tensor] = None,
+                   interleaved: bool = True) -> None:
     """proj [T, H*(d+r) + rank + r]: every head's plain (d) and rotated (r) query channels, then the low-rank
     vector and the key part all heads share.  Writes the plain query parts into q_plain [T, H*d], the rotated
     ones into the last r channels of every head of q_full [T, H*(rank+r)], and the cache row of the token
-    (the low-rank vector normed with c_weight, then the rotated shared key part) at slot_of_token[t]."""
-    require_cuda(proj, c_weight, positions, cos, sin, slot_of_token, cache, q_plain, q_full)
+    (the low-rank vector normed with c_weight, then the rotated shared key part) at slot_of_token[t].
+    With `low` [T, rank + r] (of proj's dtype, unit column stride) proj holds the queries only, [T, H*(d+r)].
+    `interleaved`: the rotary pairs are channels (2i, 2i+1); else (i, i + r/2)."""
+    require_cuda(proj, c_weight, positions, cos, sin, slot_of_token, cache, q_plain, q_full, low)
     _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
     T, H, d, r = proj.shape[0], num_heads, head_dim, rot_dim
-    if proj.stride(1) != 1 or proj.shape[1] != H * (d + r) + rank + r:
-        raise KernelError(f"latent_prepare: proj is [T, {H * (d + r) + rank + r}] with unit column stride")
+    cols = H * (d + r) + (0 if low is not None else rank + r)
+    if proj.stride(1) != 1 or proj.shape[1] != cols:
+        raise KernelError(f"latent_prepare: proj is [T, {cols}] with unit column stride")
+    if low is not None and (low.dtype != proj.dtype or low.shape != (T, rank + r) or low.stride(1) != 1):
+        raise KernelError(f"latent_prepare: low is [T, {rank + r}] of proj's dtype with unit column stride")
     _contig(q_plain, "q_plain"); _contig(q_full, "q_full"); _contig(c_weight, "c_weight")
     if q_plain.shape != (T, H * d) or q_full.shape != (T, H * (rank + r)) or q_plain.dtype != q_full.dtype:
         raise KernelError("latent_prepare: q_plain is [T, H*d], q_full [T, H*(rank+r)], of one dtype")
@@ -1107,7 +1281,8 @@ def latent_prepare(proj: torch.Tensor, c_weight: torch.Tensor, eps: float, posit
     check(L.core().ri_latent_prepare(_p(proj), dtype_code(proj.dtype), proj.stride(0), _p(c_weight),
                                      dtype_code(c_weight.dtype), float(eps), _p(positions), _p(cos), _p(sin),
                                      _p(slot_of_token), _p(cache), _p(q_plain), _p(q_full), dtype_code(q_full.dtype),
-                                     T, H, d, r, rank, stream_ptr()), "latent_prepare")
+                                     T, H, d, r, rank, _p(low), low.stride(0) if low is not None else 0,
+                                     1 if interleaved else 0, stream_ptr()), "latent_prepare")
 
 
 def bias_rows(x: torch.Tensor, bias: torch.Tensor) -> None:

@@ -43,9 +43,9 @@ _SIGNATURES = {
     "ri_embed_rmsnorm": [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_hyper_collect": [_P, _I, _P, _I, _P, _P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _I, _I, _P],
     "ri_qkv_prepare": [_P, _I, _I, _P, _P, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
-    "ri_attention_plain_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _I, _P],
-    "ri_attention_single_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _F, _P, _I, _I, _I, _P],
-    "ri_attention_rows": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _F, _P, _I, _I, _I, _I, _P, _P],
+    "ri_attention_plain_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _F, _P, _I, _I, _I, _P, _P],
+    "ri_attention_single_ex": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _P, _F, _P, _I, _I, _I, _P, _P],
+    "ri_attention_rows": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _F, _P, _I, _I, _I, _I, _P, _P, _P],
     "ri_attention_rows_tokens_per_tile": [_I, _I, _I],
     "ri_attention_rows_ctas_per_sm": [_I, _I],
     "ri_embed_scaled": [_P, _P, _I, _F, _P, _I, _I, _I, _P],
@@ -53,12 +53,12 @@ _SIGNATURES = {
     "ri_scale_add_norm": [_P, _P, _I, _P, _F, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_row_norm_gate": [_P, _P, _I, _I, _P, _I, _F, _P, _I, _I, _I, _P],
     "ri_diff_combine": [_P, _F, _F, _F, _P, _I, _I, _P, _I, _I, _I, _I, _P],
-    "ri_latent_prepare": [_P, _I, _I, _P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ri_latent_prepare": [_P, _I, _I, _P, _I, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P],
     "ri_bias_rows": [_P, _I, _P, _I, _I, _I, _P],
     "ri_activation_cols": [_P, _I, _I, _I, _I, _I, _P],
-    "ri_moe_route": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ri_moe_route": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _I, _P],
     "ri_moe_sort": [_P, _P, _I, _I, _P, _P, _P, _P],
-    "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "ri_moe_gather": [_P, _P, _I, _P, _I, _I, _P],
     "ri_gemm_tc_grouped": [_P, _P, _I, _I, _I, _P, _I, _I, _P, _I, _P, _P],
     "ri_moe_combine": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P],
@@ -71,12 +71,19 @@ _SIGNATURES = {
     "ri_scaled_sum": [_P, _P, _F, _F, _P, _I, _L, _P],
     "ri_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ri_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "ri_rms_sandwich": [_P, _I, _P, _I, _I, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "ri_short_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "ri_rglru_gates": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
+    "ri_rglru_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "ri_sigmoid_gate": [_P, _I, _I, _P, _I, _I, _P, _I, _I, _I, _P],
+    "ri_softcap": [_P, _L, _F, _P],
+    "ri_glu_pairs": [_P, _P, _I, _L, _I, _F, _F, _P],
     "ri_gated_decay": [_P, _P, _I, _F, _I, _I, _P],
     "ri_delta_prepare": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _F, _F, _P, _P, _I, _I, _I, _P],
 }
 
 _CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu", "sequence_parts.cu", "stream_parts.cu",
-                 "mixture_parts.cu", "postnorm_parts.cu"]
+                 "mixture_parts.cu", "postnorm_parts.cu", "depth_parts.cu"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 
 

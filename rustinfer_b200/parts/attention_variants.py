@@ -87,10 +87,11 @@ class PlainAttend:
         return max(1, min(self.slots // ctas, -(-self._span(max_kv_len) // 128), self.ROWS_MAX_SPLITS))
 
     def __call__(self, q: torch.Tensor, out: torch.Tensor, step: StepContext, cache: PagedLayerCache, scale: float,
-                 softcap: Optional[float] = None, sink_values: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 softcap: Optional[float] = None, sink_values: Optional[torch.Tensor] = None,
+                 slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
         g = step.groups[cache.group]
         opts = dict(value_dim=self.vd, sink=sink_values is not None, softcap=softcap, sink_values=sink_values,
-                    maps=self.maps, value_in_key=self.value_in_key)
+                    maps=self.maps, value_in_key=self.value_in_key, slopes=slopes)
         if self._single is not None:
             (single,) = step.index(self._single)
             if single.numel() and self.fast_single:
@@ -234,7 +235,10 @@ class DifferentialAttention(Mixer):
 class LatentAttention(Mixer):
     """params: hidden_size, num_heads, head_dim (plain query/key channels of a head), rot_dim (rotated ones),
     value_dim, kv_rank, scale, rot_base, norm_eps, sink (the softmax's denominator holds exp(sink_h), a
-    learned number per head), tensor_names.
+    learned number per head), q_rank (None: q = W_q h; else queries go through a low-rank vector of that size,
+    c_q = rmsnorm(W_dq h) * `dq.norm`, q = W_uq c_q), rot_layout ("interleaved", the default: channels (2i, 2i+1)
+    turn together; "half": (i, i + rot_dim/2)), gate (the heads' outputs are multiplied element by element with
+    sigmoid(W_g h) before W_o), tensor_names.
 
     q = W_q h, per head [head_dim plain, rot_dim rotated].  W_dkv h = [kv_rank, rot_dim]: the first part,
     RMS-normed with `dkv.norm`, is the latent c; the second, rotated, is a key part all heads share.  A
@@ -255,6 +259,11 @@ class LatentAttention(Mixer):
         self.rot_base = float(p.get("rot_base", 10000.0))
         self.norm_eps = float(p["norm_eps"])
         self.sink = bool(p.get("sink", False))
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") else None
+        self.rot_layout = str(p.get("rot_layout", "interleaved"))
+        if self.rot_layout not in ("half", "interleaved"):
+            raise ValueError(f"rot_layout {self.rot_layout!r}: known are 'half' and 'interleaved'")
+        self.gate = bool(p.get("gate", False))
         self.tensor_names = dict(p.get("tensor_names") or {})
         self.kd = self.rank + self.rd                       # a cached row
         if self.rd % 2 or self.rd < 0:
@@ -267,10 +276,18 @@ class LatentAttention(Mixer):
 
     def param_decls(self) -> Dict[str, ParamDecl]:
         n = self._name
-        d = {n("q"): ParamDecl((self.H * (self.hd + self.rd), self.hidden)),
-             n("dkv"): ParamDecl((self.kd, self.hidden)), n("dkv.norm"): ParamDecl((self.rank,), init="ones"),
+        nq = self.H * (self.hd + self.rd)
+        d = {n("dkv"): ParamDecl((self.kd, self.hidden)), n("dkv.norm"): ParamDecl((self.rank,), init="ones"),
              n("uk"): ParamDecl((self.H * self.hd, self.rank)), n("uv"): ParamDecl((self.H * self.vd, self.rank)),
              n("o"): ParamDecl((self.hidden, self.H * self.vd))}
+        if self.q_rank:
+            d[n("dq")] = ParamDecl((self.q_rank, self.hidden))
+            d[n("dq.norm")] = ParamDecl((self.q_rank,), init="ones")
+            d[n("uq")] = ParamDecl((nq, self.q_rank))
+        else:
+            d[n("q")] = ParamDecl((nq, self.hidden))
+        if self.gate:
+            d[n("g")] = ParamDecl((self.H * self.vd, self.hidden))
         if self.sink:
             d[n("sink")] = ParamDecl((self.H,), init="zeros")
         return d
@@ -283,16 +300,22 @@ class LatentAttention(Mixer):
         self.attend = PlainAttend(ctx, self.H, 1, self.kd, self.rank, value_in_key=True)
         self.position = _shared_position(ctx, PartSpec("rope", {
             "head_dim": self.rd, "rotary_dim": self.rd, "theta": self.rot_base, "scaling": None,
-            "layout": "interleaved"})) if self.rd else None
+            "layout": self.rot_layout})) if self.rd else None
 
     def step_indices(self):
         return self.attend.step_indices()
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         n = self._name
-        parts = [tensors[n("q")], tensors[n("dkv")]]
+        # one product for everything that reads the mixer's input: queries (or their low-rank vector), the
+        # cached row, the gate
+        parts = [tensors[n("dq") if self.q_rank else n("q")], tensors[n("dkv")]] + ([tensors[n("g")]] if self.gate else [])
         dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
         self.proj = Linear(torch.cat([t.to(dt) for t in parts], dim=0), self.ctx.num_sms)
+        self.uq = self.q_norm = None
+        if self.q_rank:
+            self.uq = Linear(tensors[n("uq")], self.ctx.num_sms)
+            self.q_norm = tensors[n("dq.norm")].to(torch.float32).contiguous()
         self.c_norm = tensors[n("dkv.norm")].contiguous()
         act = self.ctx.dtype
         self.w_uk = tensors[n("uk")].to(act).view(self.H, self.hd, self.rank).contiguous()
@@ -309,9 +332,17 @@ class LatentAttention(Mixer):
         q_plain = torch.empty((T, H * self.hd), dtype=dt, device=x.device)
         q_full = torch.empty((T, H * self.kd), dtype=dt, device=x.device)
         cos, sin = (self.position.cos, self.position.sin) if self.position is not None else (self._no_rot, self._no_rot)
-        K.latent_prepare(proj, self.c_norm, self.norm_eps, step.positions, cos, sin,
+        nq = self.q_rank or H * (self.hd + self.rd)
+        if self.q_rank:
+            cq = torch.empty((T, self.q_rank), dtype=dt, device=x.device)
+            K.rms_sandwich(proj[:, :nq], None, None, None, self.q_norm, cq, self.norm_eps)
+            queries, low = self.uq(cq, out_dtype=torch.float32), proj[:, nq: nq + self.kd]
+        else:
+            queries, low = proj[:, : nq + self.kd], None
+        K.latent_prepare(queries, self.c_norm, self.norm_eps, step.positions, cos, sin,
                          g.slot_of_token if cache.writes else None, cache.kv if cache.writes else None,
-                         q_plain, q_full, H, self.hd, self.rd, self.rank)
+                         q_plain, q_full, H, self.hd, self.rd, self.rank, low=low,
+                         interleaved=self.rot_layout == "interleaved")
         # q' of every head into the first kv_rank channels of its row of q_full
         torch.bmm(q_plain.view(T, H, self.hd).transpose(0, 1), self.w_uk,
                   out=q_full.view(T, H, self.kd)[:, :, : self.rank].transpose(0, 1))
@@ -319,4 +350,92 @@ class LatentAttention(Mixer):
         self.attend(q_full, lat, step, cache, self.scale, sink_values=self.sink_values)
         y = torch.empty((T, H * self.vd), dtype=dt, device=x.device)
         torch.bmm(lat.view(T, H, self.rank).transpose(0, 1), self.w_uv, out=y.view(T, H, self.vd).transpose(0, 1))
+        if self.gate:
+            gated = torch.empty_like(y)
+            K.sigmoid_gate(y, proj[:, nq + self.kd:], 1, gated)
+            y = gated
+        return self.o(y, out_dtype=torch.float32)
+
+
+@register_mixer("distance_bias_attention")
+class DistanceBiasAttention(Mixer):
+    """Grouped-query attention without rotation, whose scores carry a linear distance bias:
+
+        score(i, j) = q_i . k_j * scale - slope_h * (i - j),    slope_h = 2^(-slope_exponent * (h + 1) / H)
+
+    for head h of H, over the keys of a sliding window (None: every earlier key).  params: hidden_size, num_heads,
+    num_kv_heads, head_dim, value_dim, scale, window, slope_exponent (default 8), sink (the softmax's denominator
+    holds exp(sink_h), a learned number per head with no key or value), head_gate (head h's output is multiplied
+    by sigmoid of the h-th of H numbers W_g x), tensor_names.  Tensors: q, k, v, o, and `sink` [H], `g` [H, hidden]
+    where asked for; no biases.  q, k, v and the gates are one product of the input; scores, softmax weights and
+    their product with the values are fp32 in both engines (the kernels `PlainAttend` picks)."""
+    graph_safe = True
+
+    def __init__(self, params):
+        super().__init__(params)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.H, self.G = int(p["num_heads"]), int(p.get("num_kv_heads") or p["num_heads"])
+        self.hd, self.vd = int(p["head_dim"]), int(p.get("value_dim") or p["head_dim"])
+        self.scale = float(p["scale"])
+        self.window = int(p["window"]) if p.get("window") else None
+        self.slope_exponent = float(p.get("slope_exponent", 8.0))
+        self.sink, self.head_gate = bool(p.get("sink", False)), bool(p.get("head_gate", False))
+        self.tensor_names = dict(p.get("tensor_names") or {})
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads are not a multiple of {self.G} kv heads")
+        if not (1 <= self.hd <= 512 and 1 <= self.vd <= 512):
+            raise ValueError(f"head sizes {self.hd}, {self.vd}: the attention kernel takes sizes up to 512")
+        self.nq, self.nk, self.nv = self.H * self.hd, self.G * self.hd, self.G * self.vd
+
+    def _name(self, local: str) -> str:
+        return self.tensor_names.get(local, local)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        n = self._name
+        d = {n("q"): ParamDecl((self.nq, self.hidden)), n("k"): ParamDecl((self.nk, self.hidden)),
+             n("v"): ParamDecl((self.nv, self.hidden)), n("o"): ParamDecl((self.hidden, self.H * self.vd))}
+        if self.sink:
+            d[n("sink")] = ParamDecl((self.H,), init="zeros")
+        if self.head_gate:
+            d[n("g")] = ParamDecl((self.H, self.hidden))
+        return d
+
+    def cache_need(self):
+        return PagedKV(self.G, self.hd, self.window, value_dim=self.vd if self.vd != self.hd else None)
+
+    def prepare(self, ctx: BuildContext) -> None:
+        super().prepare(ctx)
+        self.attend = PlainAttend(ctx, self.H, self.G, self.hd, self.vd, window=self.window)
+        slopes = [2.0 ** (-self.slope_exponent * (h + 1) / self.H) for h in range(self.H)]
+        self.slopes = torch.tensor(slopes, dtype=torch.float64).to(torch.float32).to(ctx.device)
+
+    def step_indices(self):
+        return self.attend.step_indices()
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        n = self._name
+        parts = [tensors[n(x)] for x in (("q", "k", "v", "g") if self.head_gate else ("q", "k", "v"))]
+        dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
+        self.proj = Linear(torch.cat([t.to(dt) for t in parts], dim=0), self.ctx.num_sms)
+        self.o = Linear(tensors[n("o")], self.ctx.num_sms)
+        self.sink_values = tensors[n("sink")].to(torch.float32).contiguous() if self.sink else None
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache) -> torch.Tensor:
+        T, dt = x.shape[0], self.ctx.dtype
+        g = step.groups[cache.group]
+        proj = self.proj(x, out_dtype=torch.float32)
+        nqkv = self.nq + self.nk + self.nv
+        q = torch.empty((T, self.nq), dtype=dt, device=x.device)
+        K.qkv_prepare(proj[:, :nqkv], None, None, None, 0, 0.0, step.positions, None, None, 0, False,
+                      g.slot_of_token if cache.writes else None, cache.kv if cache.writes else None, q,
+                      self.H, self.G, self.hd, self.vd, True)
+        if self.head_gate:
+            o = torch.empty((T, self.H * self.vd), dtype=torch.float32, device=x.device)
+            self.attend(q, o, step, cache, self.scale, sink_values=self.sink_values, slopes=self.slopes)
+            y = torch.empty((T, self.H * self.vd), dtype=dt, device=x.device)
+            K.sigmoid_gate(o, proj[:, nqkv:], self.vd, y)
+        else:
+            y = torch.empty((T, self.H * self.vd), dtype=dt, device=x.device)
+            self.attend(q, y, step, cache, self.scale, sink_values=self.sink_values, slopes=self.slopes)
         return self.o(y, out_dtype=torch.float32)

@@ -33,7 +33,8 @@ from .spec import PartSpec
 @dataclass(frozen=True)
 class ParamDecl:
     """A tensor a part owns: its shape, how the random-weights mode fills it
-    ("normal": N(0, std); "ones" / "zeros" / "identity": 1 / 0 / the unit matrix, plus N(0, std) when norms are perturbed).  A size
+    ("normal": N(0, std); "ones" / "zeros" / "identity" / "depth_last": 1 / 0 / the unit matrix / a vector of zeros that
+    ends in 1, plus N(0, std) when norms are perturbed).  A size
     of -1 is one that only the file's tensor gives (the rank of a low-rank pair, say)."""
     shape: Tuple[int, ...]
     init: str = "normal"

@@ -24,6 +24,11 @@ class Hidden:
     pending: Optional[torch.Tensor]     # [T, hidden] activation dtype, not yet added
     fresh: bool = False                 # several streams of which only the first is written yet (all are equal)
     act: Optional[torch.Tensor] = None  # the stream rounded to the activation dtype, where a block keeps one
+    # a model whose layers read a weighted average of all earlier results: [results, T, hidden] fp32 (entry 0 the
+    # stem's output), how many entries are written, and the buffer the averages go to
+    history: Optional[torch.Tensor] = None
+    depth: int = 0
+    average: Optional[torch.Tensor] = None
 
 
 class Block:
@@ -142,8 +147,83 @@ def _post_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
     hidden.act = x
 
 
+@dataclass
+class DepthPending:
+    """The end of a layer of the `sandwich_depth_average` arrangement that has not run yet: the last sublayer's
+    output is normed and added to the stream, the sum is the layer's result (entry `n_prev` of the history), and
+    the weighted average of all results so far is what the next reader gets.  The next norm that reads the stream
+    (of the next layer, or the model's last) runs this together with itself, in one kernel."""
+    h_in: torch.Tensor
+    delta: torch.Tensor
+    post_w: torch.Tensor
+    result: torch.Tensor                # history[n_prev]
+    history: torch.Tensor
+    n_prev: int
+    weights: torch.Tensor               # fp32 [n_prev + 1]
+    avg_out: torch.Tensor
+    eps: float
+
+    def run(self, next_w: Optional[torch.Tensor], out: Optional[torch.Tensor]) -> None:
+        from ..ops import kernels as K
+        K.rms_sandwich(self.h_in, self.delta, self.post_w, self.result, next_w, out, self.eps, history=self.history,
+                       n_prev=self.n_prev, dwa=self.weights, avg_out=self.avg_out)
+
+
+def settle_depth(hidden: Hidden) -> torch.Tensor:
+    """Run what a layer of `sandwich_depth_average` left pending; returns the stream (the depth average)."""
+    if isinstance(hidden.pending, DepthPending):
+        hidden.pending.run(None, None)
+        hidden.pending = None
+    return hidden.stream
+
+
+def _sandwich_depth_average(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    """A norm before and after each sublayer, and a weighted average over depth.  With x the layer's input:
+
+        x <- x + post_mixer_norm(mixer(mixer_norm(x)));  x <- x + post_ffn_norm(ffn(ffn_norm(x)))
+
+    (the second only when the layer has a feed-forward; the post norms hold the residual's factor as their
+    `scale`).  x is then the layer's result X_n, kept in the model's history beside X_0 (the stem's output) and the
+    earlier results, and the next layer's input (after the last layer, the final norm's) is sum_j w[j] X_j over
+    j = 0 .. n with the weights of this layer's `depth_average` part.  All norms are `rmsnorm` parts.  A mixer that
+    sets `input_float32` gets its norm's output unrounded."""
+    from ..ops import kernels as K
+    post_mixer, post_ffn = block.extra_norms.get("post_mixer_norm"), block.extra_norms.get("post_ffn_norm")
+    avg = block.extra_norms.get("depth_average")
+    if block.mixer_norm is None or post_mixer is None or avg is None:
+        raise ValueError("the sandwich_depth_average arrangement wants a norm before and after the mixer and a "
+                         "depth_average part")
+    if hidden.history is None or hidden.average is None:
+        raise ValueError("the sandwich_depth_average arrangement runs in a model whose spec sets depth_average")
+    n = hidden.depth                      # this layer's result is entry n of the history
+    if avg.count != n + 1:
+        raise ValueError(f"the layer's depth_average has {avg.count} weights; {n + 1} results exist after it")
+    x_in = hidden.stream
+    want = torch.float32 if getattr(block.mixer, "input_float32", False) else None
+    x = block.mixer_norm.add_norm(x_in, hidden.pending, out_dtype=want)
+    hidden.pending = None
+    y = block.mixer.forward(x, step, cache)
+    result = hidden.history[n]
+    if block.ffn is None:
+        last_in, last_y, last_post = x_in, y, post_mixer
+    else:
+        if block.ffn_norm is None or post_ffn is None:
+            raise ValueError("the sandwich_depth_average arrangement wants a norm before and after the feed-forward")
+        x2 = torch.empty((x_in.shape[0], x_in.shape[1]), dtype=block.ffn_norm.ctx.dtype, device=x_in.device)
+        if post_mixer.eps == block.ffn_norm.eps:
+            K.rms_sandwich(x_in, y, post_mixer.weight32, result, block.ffn_norm.weight32, x2, post_mixer.eps)
+        else:
+            post_mixer.add_into(x_in, y, h_out=result)
+            K.rms_sandwich(result, None, None, None, block.ffn_norm.weight32, x2, block.ffn_norm.eps)
+        last_in, last_y, last_post = result, block.ffn.forward(x2, step), post_ffn
+    hidden.pending = DepthPending(last_in, last_y, last_post.weight32, result, hidden.history, n, avg.weights,
+                                  hidden.average, last_post.eps)
+    hidden.stream = hidden.average
+    hidden.depth = n + 1
+
+
 ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm, "sandwich": _sandwich, "hyper": _hyper,
-                                     "post_norm": _post_norm}
+                                     "post_norm": _post_norm, "sandwich_depth_average": _sandwich_depth_average}
 
 
 def register_arrangement(name: str, fn: Callable) -> None:

@@ -7,6 +7,10 @@ chosen by a router, and through a shared one where the model has it.
     the `top` largest c are chosen; their weights are the s (divided by their sum when `renormalize`)
     y = sum_chosen weight_e * down_e( silu(gate_e x) * up_e x ) + shared(x)
 
+With `score` "softmax_chosen" the `top` largest logits z are chosen as they are and the weights are their softmax
+among themselves.  With `activation` "clamped" an expert is down_e( g' sigmoid(alpha g') (u' + 1) ) with
+g' = min(gate_e x, limit) and u' = clamp(up_e x, -limit, limit).
+
 The router's product, scores and choice are fp32.  The (token, choice) pairs are sorted by expert on the
 device and the experts' products run over the sorted rows; no count visits the host, so the part can be
 captured in a step's CUDA graph.  The reference engine has dense feed-forwards only
@@ -27,7 +31,8 @@ from .spec import PartSpec
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
     """params: hidden_size, expert_ff, experts, top, groups_count / groups_keep (None: no groups), shared_ff
-    (None: no shared expert), score ("sigmoid"), correction (the router has a tensor added to the scores for
+    (None: no shared expert), score ("sigmoid", or "softmax_chosen"), activation ("silu", or "clamped" with
+    `limit` and `alpha`, default 1.702), correction (the router has a tensor added to the scores for
     the choice), renormalize, output ("float32", the default, or the activation dtype); tensor names:
     expert_prefix (default "e{}."; `{}` is the expert's number), gate_name / up_name / down_name (default
     "gate" / "up" / "down"), router_name ("router"), correction_name ("correction"), shared_prefix ("shared.")."""
@@ -42,8 +47,16 @@ class RoutedExperts(FeedForward):
         self.groups = int(p["groups_count"]) if p.get("groups_count") else 0
         self.keep = int(p["groups_keep"]) if p.get("groups_keep") else 0
         self.shared_ff = int(p["shared_ff"]) if p.get("shared_ff") else None
-        if str(p.get("score", "sigmoid")) != "sigmoid":
-            raise ValueError("the router's scores are sigmoids; no other kind is built")
+        self.score = str(p.get("score", "sigmoid"))
+        if self.score not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"router score {self.score!r}: known are 'sigmoid' and 'softmax_chosen'")
+        activation = str(p.get("activation", "silu"))
+        if activation not in ("silu", "clamped"):
+            raise ValueError(f"expert activation {activation!r}: known are 'silu' and 'clamped'")
+        # (limit, alpha) of the clamped pair, None for silu(gate) * up
+        self.act = (float(p["limit"]), float(p.get("alpha", 1.702))) if activation == "clamped" else None
+        if self.act is not None and not self.act[0] > 0:
+            raise ValueError("the clamp's limit is positive")
         self.has_correction = bool(p.get("correction", False))
         self.renorm = bool(p.get("renormalize", False))
         self.out_fp32 = str(p.get("output", "float32")) == "float32"
@@ -112,7 +125,7 @@ class RoutedExperts(FeedForward):
         ids = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
         K.moe_route(None, self.correction, self.top, self.groups, self.keep, self.renorm, ids, weights, self.counts,
-                    x=x if x.is_contiguous() else x.contiguous(), router=self.router)
+                    x=x if x.is_contiguous() else x.contiguous(), router=self.router, score=self.score)
         return ids, weights
 
     def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
@@ -132,10 +145,15 @@ class RoutedExperts(FeedForward):
             # tiles of 128 rows that never cross from one expert's rows into the next one's results
             xs = torch.empty((N, self.hidden), dtype=torch.bfloat16, device=dev)
             K.moe_gather(xin, order, self.top, xs)
-            K.gemm_tc_grouped(xs, self.gate_up, mid, offsets, K.EPI_SILU)
+            if self.act is None:
+                K.gemm_tc_grouped(xs, self.gate_up, mid, offsets, K.EPI_SILU)
+            else:                                          # the pairs leave the product in fp32; a kernel of its own clamps them
+                pairs = torch.empty((N, 2 * self.ff), dtype=torch.float32, device=dev)
+                K.gemm_tc_grouped(xs, self.gate_up, pairs, offsets, K.EPI_F32)
+                K.glu_pairs(pairs, mid, self.act)
             K.gemm_tc_grouped(mid, self.down, Y, offsets, K.EPI_F32)
         else:
-            K.moe_product(xin, self.gate_up, mid, offsets, order, self.top, gated=True)
+            K.moe_product(xin, self.gate_up, mid, offsets, order, self.top, gated=True, act=self.act)
             K.moe_product(mid, self.down, Y, offsets, None, self.top, gated=False)
         shared = self.shared.forward(x, step) if self.shared is not None else None
         out = torch.empty((T, self.hidden), dtype=torch.float32 if self.out_fp32 else self.ctx.dtype, device=dev)

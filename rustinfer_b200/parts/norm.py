@@ -15,26 +15,70 @@ from .base import Norm, ParamDecl, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps, weight_name (the tensor's local name, default "weight")."""
+    """params: size, eps, weight_name (the tensor's local name, default "weight"), offset (added to the stored
+    weight: 1 for a weight stored around zero; default 0), scale (a factor on the norm's output, the residual's
+    factor of a norm that follows a sublayer, say; default 1).  With an offset or a scale the part keeps
+    (offset + w) * scale in fp32.
+
+    `add_norm` takes as `delta` a tensor (added as it is), None, a `NormedDelta` (normed by the RMS norm it names,
+    then added) or a `DepthPending` (see parts/block.py); the last two run as one kernel with this norm."""
 
     def __init__(self, params):
         super().__init__(params)
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.weight_name = str(params.get("weight_name", "weight"))
+        self.offset = float(params.get("offset", 0.0))
+        self.scale = float(params.get("scale", 1.0))
         self.weight: Optional[torch.Tensor] = None
+        self._weight32: Optional[torch.Tensor] = None
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        return {self.weight_name: ParamDecl((self.size,), init="ones")}
+        return {self.weight_name: ParamDecl((self.size,), init="zeros" if self.offset == 1.0 else "ones")}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.weight_name].contiguous()
+        w = tensors[self.weight_name].contiguous()
+        if self.offset != 0.0 or self.scale != 1.0:
+            w = ((w.to(torch.float32) + self.offset) * self.scale).contiguous()
+        self.weight = w
+        self._weight32 = None
 
-    def add_norm(self, h, delta, rows=None):
+    @property
+    def weight32(self) -> torch.Tensor:
+        if self._weight32 is None:
+            self._weight32 = self.weight.to(torch.float32).contiguous()
+        return self._weight32
+
+    def add_norm(self, h, delta, rows=None, out_dtype=None):
+        from .block import DepthPending
         n = h.shape[0] if rows is None else rows.numel()
-        out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=h.device)
+        out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=h.device)
+        if isinstance(delta, DepthPending):
+            if rows is None and delta.eps == self.eps:
+                delta.run(self.weight32, out)
+            else:
+                delta.run(None, None)
+                K.rms_sandwich(delta.avg_out, None, None, None, self.weight32, out, self.eps, rows=rows)
+            return out
+        if isinstance(delta, NormedDelta):
+            post = delta.norm
+            if rows is None and post.eps == self.eps:
+                K.rms_sandwich(h, delta.delta, post.weight32, h, self.weight32, out, self.eps)
+            else:
+                post.add_into(h, delta.delta)
+                K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows)
+            return out
+        if self.weight.dtype == torch.float32 and (delta is None or delta.dtype != out.dtype or self.ctx.dtype != out.dtype):
+            if delta is not None:
+                K.residual_add(h, delta)
+            K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows)
+            return out
         K.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         return out
+
+    def add_into(self, h: torch.Tensor, delta: torch.Tensor, h_out: Optional[torch.Tensor] = None) -> None:
+        """h_out (default h itself) <- h + rms(delta) * w."""
+        K.rms_sandwich(h, delta, self.weight32, h if h_out is None else h_out, None, None, self.eps)
 
 
 @register_norm("post_rmsnorm")
@@ -79,7 +123,7 @@ class NormedDelta:
     """A sublayer's output that is to pass through `norm` before it is added to the stream (a
     block with a norm after each sublayer leaves this as its pending delta)."""
     delta: torch.Tensor
-    norm: "LayerNorm"
+    norm: Norm                          # a `layernorm` or an `rmsnorm`; the norm that adds it is of the same kind
 
 
 @register_norm("layernorm")
@@ -133,3 +177,26 @@ class LayerNorm(Norm):
     def add_into(self, h: torch.Tensor, delta: torch.Tensor) -> None:
         """h += LN(delta)."""
         K.sandwich_norm(h, delta, self.weight, self.bias, None, None, None, self.eps)
+
+
+@register_norm("depth_average")
+class DepthAverage(Norm):
+    """The weights of a layer's average over depth (see the `sandwich_depth_average` arrangement): `count` numbers,
+    one for the stem's output and one for every layer's result up to this layer's own.  params: count,
+    weight_name (default "weight").  It norms nothing; it stands among a block's norms because, like them, it is a
+    small tensor of the block that the kernel around the sublayers reads."""
+
+    def __init__(self, params):
+        super().__init__(params)
+        self.count = int(params["count"])
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.weights: Optional[torch.Tensor] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {self.weight_name: ParamDecl((self.count,), init="depth_last")}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weights = tensors[self.weight_name].to(torch.float32).contiguous()
+
+    def add_norm(self, h, delta, rows=None):
+        raise TypeError("depth_average holds weights only: it runs in the `sandwich_depth_average` block arrangement")

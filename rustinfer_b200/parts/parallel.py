@@ -27,9 +27,9 @@ class ParallelMixers(Mixer):
         self.sides: List[Mixer] = [MIXERS.build(params["left"]), MIXERS.build(params["right"])]
         self.scales = [float(params.get("left_scale", 1.0)), float(params.get("right_scale", 1.0))]
         self.prefixes = [str(params.get("left_prefix", "left.")), str(params.get("right_prefix", "right."))]
+        # a side's needs as a tuple (a side may itself keep several things: a state beside a convolution's inputs)
         self._needs = [m.cache_need() for m in self.sides]
-        if any(isinstance(n, (tuple, list)) for n in self._needs):
-            raise ValueError("a side of parallel_mixers is a single mixer, not another pair")
+        self._counts = [0 if n is None else len(n) if isinstance(n, (tuple, list)) else 1 for n in self._needs]
 
     @property
     def graph_safe(self) -> bool:
@@ -39,7 +39,7 @@ class ParallelMixers(Mixer):
         return {pre + name: d for pre, m in zip(self.prefixes, self.sides) for name, d in m.param_decls().items()}
 
     def cache_need(self):
-        needs = tuple(n for n in self._needs if n is not None)
+        needs = tuple(x for n in self._needs if n is not None for x in (n if isinstance(n, (tuple, list)) else (n,)))
         return needs or None
 
     def step_indices(self) -> Sequence[StepIndex]:
@@ -57,8 +57,12 @@ class ParallelMixers(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
         caches = list(cache) if isinstance(cache, (tuple, list)) else [cache]
         outs = []
-        for m, need in zip(self.sides, self._needs):
-            outs.append(m.forward(x, step, caches.pop(0) if need is not None else None))
+        for m, need, count in zip(self.sides, self._needs, self._counts):
+            mine = [caches.pop(0) for _ in range(count)]
+            outs.append(m.forward(x, step, None if need is None else tuple(mine) if isinstance(need, (tuple, list))
+                                  else mine[0]))
+        if outs[0].dtype != outs[1].dtype:                   # one side leaves in 32-bit, the other rounded
+            outs = [o.to(torch.float32) for o in outs]
         out = torch.empty_like(outs[0])
         K.scaled_sum(outs[0], outs[1], self.scales[0], self.scales[1], out)
         return out

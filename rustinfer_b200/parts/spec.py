@@ -79,6 +79,9 @@ class ModelSpec:
     # 0: one residual stream [tokens, hidden]; n >= 1: n streams [n, tokens, hidden] that the `hyper`
     # block arrangement reads through weighted sums and the last norm adds up
     streams: int = 0
+    # True: every layer's result is kept for the step ([results, tokens, hidden] fp32) and a layer's input is a
+    # weighted average of all earlier results (the `sandwich_depth_average` block arrangement)
+    depth_average: bool = False
 
     def embed_spec(self) -> PartSpec:
         return self.embed or PartSpec("token_embedding", {"vocab_size": self.vocab_size,

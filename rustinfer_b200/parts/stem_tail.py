@@ -120,13 +120,15 @@ class NormedEmbedding(TokenEmbedding):
 @register_head("linear_head")
 class LinearHead(Head):
     """params: vocab_size, hidden_size, tied (the configuration says the head is the embedding
-    table: the file need not have a weight for it), weight_name (the tensor's local name, default "weight")."""
+    table: the file need not have a weight for it), weight_name (the tensor's local name, default "weight"),
+    softcap (c > 0: logits <- c * tanh(logits / c); None: none)."""
 
     def __init__(self, params):
         super().__init__(params)
         self.vocab, self.hidden = int(params["vocab_size"]), int(params["hidden_size"])
         self.tied = bool(params.get("tied", False))
         self.weight_name = str(params.get("weight_name", "weight"))
+        self.softcap = float(params["softcap"]) if params.get("softcap") else None
         self.linear: Optional[Linear] = None
         self.is_tied = False
 
@@ -144,4 +146,8 @@ class LinearHead(Head):
         self.linear = Linear(w, self.ctx.num_sms)
 
     def forward(self, normed: torch.Tensor) -> torch.Tensor:
-        return self.linear(normed, out_dtype=torch.float32)
+        logits = self.linear(normed, out_dtype=torch.float32)
+        if self.softcap:
+            logits = logits.contiguous()
+            K.softcap(logits, self.softcap)
+        return logits

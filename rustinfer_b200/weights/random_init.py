@@ -43,10 +43,12 @@ def random_tensors(config: Mapping[str, Any], seed: int, std: float = 0.02, norm
             continue
         g = _generator(seed, name)
         shape = tuple(FREE_SIZE if n == -1 else n for n in d.shape)    # a size only the file would give
-        if d.init in ("ones", "zeros", "identity"):
+        if d.init in ("ones", "zeros", "identity", "depth_last"):
             t = (torch.ones(shape, dtype=torch.float32) if d.init == "ones" else
                  torch.eye(shape[0], shape[1], dtype=torch.float32) if d.init == "identity" else
                  torch.zeros(shape, dtype=torch.float32))
+            if d.init == "depth_last":                    # a vector whose last element is 1: the newest result alone
+                t[-1] = 1.0
             if norm_std > 0:
                 t += torch.randn(shape, generator=g, dtype=torch.float32) * norm_std
         else:
