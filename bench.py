@@ -17,7 +17,7 @@ attention), the Llama-3.2-3B-shaped model at 8 of its 28 layers serving 64 reque
 this engine's attention and GEMM kernels timed against the reference's own attention kernels
 (compiled unmodified, see baseline/reference_kernels.py) and the library GEMM on the same data.
 `--shape` takes the layer sizes of the 3B or 8B benchmark configuration for the headline instead;
-`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` (or `pikalix`, `sotazen`) leaves
+`--only decode|prefill|serve` runs one part alone and prints its time.  `--family dirurax` (or `pikalix`, `sotazen`, `linedra`) leaves
 all of that aside and prints a line of its own: prefill and decode of that family's models at two sizes beside
 Llama models of the same width, depth, feed-forward width and vocabulary, and that family's kernels alone against
 their rooflines.
@@ -984,8 +984,177 @@ def sotazen_kernels(hbm_gbs, bf16_tflops, size):
     return out
 
 
+def _linedra(width, layers, ff, vocab, attn, window, recurrent, latent, experts, top, expert_ff, taps):
+    """`layers` layers in the order parallel, parallel, parallel, latent attention (norms around the sublayers, the
+    input convolution, the depth average), routed experts with clamped pairs in each."""
+    h, kv, dim, vdim = attn
+    rw, blocks, conv = recurrent
+    th, td, tr, tv, rank, q_rank = latent
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+        if i % 4 == 3:
+            mixer = {"heads": th, "dim": td, "rot_dim": tr, "vdim": tv, "kv_rank": rank, "q_rank": q_rank,
+                     "scale": (td + tr) ** -0.5, "rot": {"dims": tr, "base": 10000.0}}
+            out.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"left": {"heads": h, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "mask": {"size": window}},
+                     "right": {"width": rw, "blocks": blocks, "conv": conv}, "left_scale": 0.6, "right_scale": 0.5}
+            out.append({"type": "parallel", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Linedra", "width": width, "vocab": vocab, "norm": {"eps": 1e-6}, "canon": {"taps": taps},
+            "embedding": {"scale": 1.0}, "residual_mult": 0.5, "logit_softcap": 30.0, "layers": out}
+
+
+# Linedra at the same widths: attention (heads, kv heads, key, value), the recurrent unit (width, blocks, taps), latent
+# attention (heads, plain, rotated, value, rank, query rank); a token's feed-forward work equals the dense one's
+# (top x expert_ff = ff).  `pikalix`: the Pikalix model of the same width, depth and vocabulary (attention with a sink
+# and a window, routed experts), the nearest of the families the engine had
+LINEDRA_SIZES = {
+    "w1024": dict(width=1024, layers=8, ff=4096, vocab=32768, attn=(16, 4, 64, 64), window=1024, recurrent=(1024, 8, 4),
+                  latent=(16, 64, 32, 64, 128, 384), experts=32, top=4, expert_ff=1024, taps=4, llama=(16, 4, 64)),
+    "w2048": dict(width=2048, layers=8, ff=8192, vocab=32768, attn=(32, 8, 64, 64), window=1024, recurrent=(2048, 16, 4),
+                  latent=(32, 64, 32, 64, 256, 768), experts=32, top=4, expert_ff=2048, taps=4, llama=(32, 8, 64)),
+}
+
+
+def linedra_kernels(hbm_gbs, bf16_tflops, size):
+    """The Linedra kernels alone at one size, each beside the like kernel of the nearest existing family on the same
+    shapes (the add + RMSNorm of the Llama path, the layer norm around a sublayer of Dirurax, the streams kernel of
+    Pikalix, the walk with fixed decays of Sotazen, the attention with a sink of Pikalix): microseconds, and what that
+    is of the bytes they must move at the measured copy bandwidth."""
+    import torch
+    from rustinfer_b200.ops import kernels as K
+    from rustinfer_b200.parts.attention_variants import PlainAttend
+    from rustinfer_b200.parts.base import BuildContext
+    dev = torch.device("cuda:0")
+    sz = LINEDRA_SIZES[size]
+    d = sz["width"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    bf = lambda *s: torch.randn(*s, device=dev).to(torch.bfloat16)
+    f32 = lambda *s: torch.randn(*s, device=dev)
+    frac = lambda moved, us: round(moved / (us * 1e-6) / 1e9 / hbm_gbs, 4)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    fma_per_s = sms * 128 * 1.9e9
+    out = {}
+    ah, akv, ad, av = sz["attn"]
+    W, blocks, taps = sz["recurrent"]
+    layers = sz["layers"]
+    for tag, T, entries in (("prefill2048", 2048, 1), ("decode64", 64, 64)):
+        cu = i32([i * (T // entries) for i in range(entries + 1)])
+        slots = i32(list(range(entries)))
+        # the norms around a sublayer beside the add + RMSNorm of the Llama path and Dirurax's layer norms
+        h, delta, pw, nw = f32(T, d), f32(T, d), f32(d), f32(d)
+        h2, xo = torch.empty(T, d, device=dev), torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.rms_sandwich(h, delta, pw, h2, nw, xo, 1e-6), flush=flush)
+        d16, w16 = bf(T, d), bf(d)
+        us_rms = time_kernel(lambda: K.add_rmsnorm(h, d16, w16, 1e-6, xo), flush=flush)
+        us_ln = time_kernel(lambda: K.sandwich_norm(h, d16, w16, w16, w16, w16, xo, 1e-6), flush=flush)
+        out[f"rms_sandwich_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * d * (4 + 4 + 4 + 2), us),
+                                      "add_rmsnorm_us": round(us_rms, 1), "add_rmsnorm_hbm_frac": frac(T * d * (4 + 4 + 2 + 2), us_rms),
+                                      "layer_sandwich_us": round(us_ln, 1), "layer_sandwich_hbm_frac": frac(T * d * (4 + 4 + 2 + 2), us_ln)}
+        # the end of a layer in the middle of the model: norm and add, the average over depth, the next layer's norm
+        n_prev = layers // 2
+        hist, dwa, avg = f32(n_prev + 1, T, d), f32(n_prev + 1), torch.empty(T, d, device=dev)
+        x32 = torch.empty(T, d, device=dev)
+        us = time_kernel(lambda: K.rms_sandwich(h, delta, pw, hist[n_prev], nw, x32, 1e-6, history=hist, n_prev=n_prev, dwa=dwa,
+                                                avg_out=avg), flush=flush)
+        streams, y = f32(2, T, d), f32(T, d)
+        mix, wr, rd = f32(2, 2), f32(2), f32(2)
+        us_h = time_kernel(lambda: K.hyper_collect(streams, False, y, mix, wr, rd, w16, 1e-6, xo, None), flush=flush)
+        out[f"depth_average_{tag}"] = {"us": round(us, 1), "earlier_results": n_prev,
+                                       "hbm_frac": frac(T * d * 4 * (n_prev + 5), us),
+                                       "streams_us": round(us_h, 1), "streams_hbm_frac": frac(T * d * (4 * 5 + 2), us_h)}
+        # the convolution in front of the mixer
+        xin, cw = f32(T, d), f32(d, sz["taps"])
+        cstate = torch.zeros(entries + 1, sz["taps"] - 1, d, device=dev)
+        us = time_kernel(lambda: K.short_conv(xin, cw, None, cstate, cu, slots, xo, entries, T // entries, True), flush=flush)
+        out[f"conv_input_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * d * (4 + 2) + 2 * entries * (sz["taps"] - 1) * d * 4, us)}
+        # the recurrent unit: gates (two block-diagonal fp32 products), the walk beside Sotazen's walk with fixed decays
+        bs = W // blocks
+        u, wa, wi = f32(T, W), bf(blocks, bs, bs), bf(blocks, bs, bs)
+        ba, bi, lam = f32(W), f32(W), f32(W)
+        a, xg = torch.empty(T, W, device=dev), torch.empty(T, W, device=dev)
+        us = time_kernel(lambda: K.rglru_gates(u, wa, wi, ba, bi, lam, 8.0, a, xg), flush=flush)
+        out[f"recurrent_gates_{tag}"] = {"us": round(us, 1), "fma_frac": round(2 * T * W * bs / (us * 1e-6) / fma_per_s, 4),
+                                         "hbm_frac": frac(T * W * 12 + 2 * W * bs * 2, us)}
+        a.uniform_(0.5, 0.99)
+        yv, sy = f32(T, W), torch.empty(T, W, device=dev, dtype=torch.bfloat16)
+        rstate = torch.zeros(entries + 1, W, device=dev)
+        us = time_kernel(lambda: K.rglru_scan(a, xg, yv, ba, rstate, cu, slots, sy, entries), flush=flush)
+        H, dk, dv = max(1, W // 128), 128, 128
+        p32 = f32(T, 2 * H * dk + H * dv)
+        decay, o = torch.full((H * dk,), 0.97, device=dev), torch.empty(T, H * dv, device=dev)
+        dstate = torch.zeros(entries + 1, H, dv, K.recurrent_state_rows(dk), device=dev)
+        us_d = time_kernel(lambda: K.decay_scan(p32[:, :H * dk], p32[:, H * dk:2 * H * dk], p32[:, 2 * H * dk:], decay, 1.0, o,
+                                                dstate, cu, slots, entries, H, dk, dv), flush=flush)
+        out[f"recurrent_walk_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * W * (12 + 2) + 2 * entries * W * 4, us),
+                                        "decay_scan_us": round(us_d, 1),
+                                        "decay_scan_hbm_frac": frac(T * (2 * H * dk + 2 * H * dv) * 4 + 2 * entries * H * dk * dv * 4, us_d)}
+        # a gate a head on the attention's output beside Sotazen's norm over all heads with its gate
+        o32, gate = f32(T, ah * av), f32(T, ah)
+        y16 = torch.empty(T, ah * av, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.sigmoid_gate(o32, gate, av, y16), flush=flush)
+        g32, wn = f32(T, ah * av), bf(ah * av)
+        us_n = time_kernel(lambda: K.row_norm_gate(o32, g32, wn, 1e-6, y16), flush=flush)
+        out[f"head_gate_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * ah * av * (4 + 2), us),
+                                   "row_norm_gate_us": round(us_n, 1), "row_norm_gate_hbm_frac": frac(T * ah * av * (4 + 4 + 2), us_n)}
+        # the clamped pairs of the experts' first product where it leaves in fp32
+        N, ff = T * sz["top"], sz["expert_ff"]
+        pairs, mid = f32(N, 2 * ff), torch.empty(N, ff, device=dev, dtype=torch.bfloat16)
+        us = time_kernel(lambda: K.glu_pairs(pairs, mid, (7.0, 1.702)), flush=flush)
+        gu16, mid2 = bf(N, 2 * ff), torch.empty(N, ff, device=dev, dtype=torch.bfloat16)
+        us_s = time_kernel(lambda: K.silu_mul(gu16, mid2), flush=flush)
+        out[f"clamped_pairs_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(N * ff * (8 + 2), us),
+                                       "silu_mul_us": round(us_s, 1), "silu_mul_hbm_frac": frac(N * ff * (4 + 2), us_s)}
+    # attention with the distance bias beside the same kernels without it (Pikalix's attention with a sink and a window)
+    B, ctx, win = 64, 4096, sz["window"]
+    nblk = ctx // PAGE
+    bctx = BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=B, num_sms=sms)
+    kv_len, cu, ent = i32([ctx] * B), i32(list(range(B + 1))), i32(list(range(B)))
+    table = torch.randperm(B * nblk, device=dev).to(torch.int32).view(B, nblk).contiguous()
+    sink = torch.zeros(ah, device=dev)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / ah) for h in range(ah)], device=dev)
+    att = PlainAttend(bctx, ah, akv, ad, av, window=win)
+    per = akv * (ad + av)
+    cache = bf(B * nblk, 2, akv, PAGE, ad) if ad == av else bf(B * nblk, PAGE * per)
+    q, o = bf(B, ah * ad), torch.empty(B, ah * av, device=dev)
+    res = {}
+    for name, sl in (("us", slopes), ("no_bias_us", None)):
+        if att.fast_single:
+            ranges = att._splits(B, ctx)
+            us = time_kernel(lambda: K.attention_single(q, o, cache, table, cu, kv_len, ent, ah, akv, ad, ad ** -0.5, win, None, av,
+                                                        sink=True, splits=ranges, part=att.part, sink_values=sink, slopes=sl), flush=flush)
+        else:
+            ranges = att._rows_splits(B, ctx) if att.rows_single else 1
+            us = time_kernel(lambda: K.attention_rows(q, o, cache, table, cu, kv_len, ent, att.zero_tok0[:B] if att.rows_single else i32([0] * B),
+                                                      ah, akv, ad, ad ** -0.5, win, av, sink=True, sink_values=sink, splits=ranges,
+                                                      part=att.part, slopes=sl), flush=flush)
+        res[name] = round(us, 1)
+    res.update(ranges=ranges, hbm_frac=frac(B * min(ctx, win) * per * 2, res["us"]),
+               no_bias_hbm_frac=frac(B * min(ctx, win) * per * 2, res["no_bias_us"]))
+    out["distance_bias_attention_decode64"] = res
+    T = 2048
+    tbl, cup, kvl = i32([list(range(T // PAGE))]), i32([0, T]), i32([T])
+    pcache = bf(T // PAGE, 2, akv, PAGE, ad) if ad == av else bf(T // PAGE, PAGE * per)
+    qp, op = bf(T, ah * ad), torch.empty(T, ah * av, device=dev)
+    pairs = sum(min(p + 1, win) for p in range(T))
+    res = {}
+    if K.attention_rows_supports(ad, av):
+        tpt = K.attention_rows_tokens_per_tile(ah, akv, ad, av)
+        tl = list(range(0, T, tpt))
+        ter, t0r = i32([0] * len(tl)), i32(tl)
+        for name, sl in (("us", slopes), ("no_bias_us", None)):
+            us = time_kernel(lambda: K.attention_rows(qp, op, pcache, tbl, cup, kvl, ter, t0r, ah, akv, ad, ad ** -0.5, win, av,
+                                                      sink=True, sink_values=sink, slopes=sl), flush=flush)
+            res[name] = round(us, 1)
+            res[name.replace("us", "useful_tflops")] = round(2 * pairs * ah * (ad + av) / (us * 1e-6) / 1e12, 2)
+    out["distance_bias_attention_prefill2048"] = res
+    return out
+
+
 def family_bench(args) -> int:
-    """`--family dirurax|pikalix|sotazen`: prefill and decode throughput of that family's models at a few sizes beside
+    """`--family dirurax|pikalix|sotazen|linedra`: prefill and decode throughput of that family's models at a few sizes beside
     Llama models of the same width, depth, feed-forward width and vocabulary (random weights), and the
     family's own kernels alone.  One JSON line."""
     import torch
@@ -998,7 +1167,7 @@ def family_bench(args) -> int:
     say = lambda msg: print(f"[bench] {msg}", file=sys.stderr, flush=True)
     ctx, tokens = min(args.context, 4096), max(2, min(args.prompt_tokens, 8192))
     family = args.family
-    table = {"pikalix": PIKALIX_SIZES, "sotazen": SOTAZEN_SIZES}.get(family, FAMILY_SIZES)
+    table = {"pikalix": PIKALIX_SIZES, "sotazen": SOTAZEN_SIZES, "linedra": LINEDRA_SIZES}.get(family, FAMILY_SIZES)
     result = {"family": family, "dtype": "bf16", "data": "synthetic", "peaks": peak_kind, "points": {}, "kernels": {}}
     sizes = [s for s in table if not args.size or s in args.size.split(",")]
     for size in sizes:
@@ -1007,9 +1176,13 @@ def family_bench(args) -> int:
             own = _pikalix(**{k: v for k, v in sz.items() if k != "llama"})
         elif family == "sotazen":
             own = _sotazen(**{k: v for k, v in sz.items() if k != "llama"})
+        elif family == "linedra":
+            own = _linedra(**{k: v for k, v in sz.items() if k != "llama"})
         else:
             own = _dirurax(sz["width"], sz["layers"], sz["ff"], sz["vocab"], sz["gla"], sz["attn"], sz["delta"], sz["block"])
         configs = {family: own, "llama": _llama_like(sz["width"], sz["layers"], sz["ff"], sz["vocab"], *sz["llama"])}
+        if family == "linedra":                      # also beside the nearest of the other families, at equal size
+            configs["pikalix"] = _pikalix(**{k: v for k, v in PIKALIX_SIZES[size].items() if k != "llama"})
         point = {}
         for fam, cfg in configs.items():
             with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
@@ -1036,9 +1209,13 @@ def family_bench(args) -> int:
                 torch.cuda.empty_cache()
         point["prefill_ratio"] = round(point[family]["prefill_tokens_per_s"] / point["llama"]["prefill_tokens_per_s"], 3)
         point["decode_ratio"] = round(point[family]["decode_tokens_per_s"] / point["llama"]["decode_tokens_per_s"], 3)
+        if "pikalix" in point and family != "pikalix":
+            point["prefill_ratio_to_pikalix"] = round(point[family]["prefill_tokens_per_s"] / point["pikalix"]["prefill_tokens_per_s"], 3)
+            point["decode_ratio_to_pikalix"] = round(point[family]["decode_tokens_per_s"] / point["pikalix"]["decode_tokens_per_s"], 3)
         result["points"][size] = point
         result["kernels"][size] = (pikalix_kernels(hbm_gbs, bf16_tflops, size) if family == "pikalix"
                                    else sotazen_kernels(hbm_gbs, bf16_tflops, size) if family == "sotazen"
+                                   else linedra_kernels(hbm_gbs, bf16_tflops, size) if family == "linedra"
                                    else dirurax_kernels(hbm_gbs, size))
         say(f"{size} kernels: {result['kernels'][size]}")
     clocks.stop()
@@ -1073,7 +1250,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
-    ap.add_argument("--family", default="llama", choices=["llama", "dirurax", "pikalix", "sotazen"],
+    ap.add_argument("--family", default="llama", choices=["llama", "dirurax", "pikalix", "sotazen", "linedra"],
                     help="dirurax, pikalix: that family's prefill and decode at a few sizes beside Llama models of equal size, "
                          "and its kernels alone (one JSON line of its own; the default workload is unchanged)")
     ap.add_argument("--size", default="", help="with --family dirurax or pikalix: sizes to run, with commas (default: all)")
@@ -1088,7 +1265,7 @@ def main() -> int:
         return 0
     args.warmup = max(args.warmup, 3)
     args.steps = max(args.steps, 2)
-    if args.family in ("dirurax", "pikalix", "sotazen"):
+    if args.family in ("dirurax", "pikalix", "sotazen", "linedra"):
         return family_bench(args)
 
     import torch

@@ -84,20 +84,31 @@ def distance_slopes(heads: int) -> torch.Tensor:
     return torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=F64)
 
 
+def attend_with_distance_bias(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                              window: Optional[int], sink: Optional[torch.Tensor]) -> torch.Tensor:
+    """q [T, H, d], k [T, G, d], v [T, G, vd]: score(i, j) = q_i . k_j * scale - slope_h (i - j) over the keys the
+    window leaves, softmax with the sink's term; [T, H, vd]."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    qh = q.permute(1, 0, 2)
+    kh = k.permute(1, 0, 2).repeat_interleave(H // G, dim=0)
+    vh = v.permute(1, 0, 2).repeat_interleave(H // G, dim=0)
+    s = (qh @ kh.transpose(1, 2)) * scale
+    i = torch.arange(T, dtype=F64)
+    s = s - distance_slopes(H)[:, None, None] * (i[:, None] - i[None, :])[None]
+    p = softmax_with_sink(s, visible(T, window), sink)
+    return (p @ vh).permute(1, 0, 2)
+
+
 def biased_window_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping) -> torch.Tensor:
     """Grouped-query attention without rotation: score = q.k * scale - slope_h (i - j) inside a window, a
     learned sink in the softmax, every head's output times sigmoid of one number of W_g h, then W_o."""
     T = h.shape[0]
     H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).reshape(T, H, d).permute(1, 0, 2)
-    k = (h @ w["k"].T).reshape(T, G, d).permute(1, 0, 2).repeat_interleave(H // G, dim=0)
-    v = (h @ w["v"].T).reshape(T, G, vd).permute(1, 0, 2).repeat_interleave(H // G, dim=0)
-    s = (q @ k.transpose(1, 2)) * m["scale"]
-    i = torch.arange(T, dtype=F64)
-    s = s - distance_slopes(H)[:, None, None] * (i[:, None] - i[None, :])[None]
+    q = (h @ w["q"].T).reshape(T, H, d)
+    k = (h @ w["k"].T).reshape(T, G, d)
+    v = (h @ w["v"].T).reshape(T, G, vd)
     window = m["mask"]["size"] if m.get("mask") else None
-    p = softmax_with_sink(s, visible(T, window), w["sink"])
-    o = (p @ v).permute(1, 0, 2)                                          # [T, H, vd]
+    o = attend_with_distance_bias(q, k, v, m["scale"], window, w["sink"])       # [T, H, vd]
     gate = torch.sigmoid(h @ w["g"].T)                                    # [T, H]
     return (o * gate[:, :, None]).reshape(T, H * vd) @ w["o"].T
 
@@ -140,8 +151,11 @@ def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], m: Mapping,
     H, d, rd, vd, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = torch.arange(T)
     base = m["rot"]["base"] if m.get("rot") else 10000.0
-    cq = rms_norm(h @ w["dq"].T, w["dq.norm"], eps)
-    q = (cq @ w["uq"].T).reshape(T, H, d + rd)
+    if "dq" in w:
+        q = rms_norm(h @ w["dq"].T, w["dq.norm"], eps) @ w["uq"].T
+    else:                                                                 # no low-rank vector: q = W_q h
+        q = h @ w["q"].T
+    q = q.reshape(T, H, d + rd)
     q_plain, q_rot = q[..., :d], rotate_half(q[..., d:], pos, rd, base)
     dkv = h @ w["dkv"].T
     c = rms_norm(dkv[:, :rank], w["dkv.norm"], eps)
@@ -230,3 +244,13 @@ def greedy(cfg: Mapping, tensors: Mapping[str, torch.Tensor], prompt: List[int],
         out.append(tok)
         seq.append(tok)
     return out
+
+
+def read_model_folder(folder: str):
+    """(config.json as a dict, tensors by name) of a model folder."""
+    import json
+    import os
+    from safetensors.torch import load_file
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(folder, "model.safetensors"))
