@@ -146,7 +146,7 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int x_stride, const 
 //   a_out = exp(log a),  x_out = sqrt(1 - a^2) * i * u          (1 - a^2 formed as -expm1(2 log a))
 // A CTA of 256 threads owns GT tokens x GN channels of one part; every sum runs over k = 0, 1, .. in order with
 // fp32 multiply-adds, so a value does not depend on which tokens share its tile.
-constexpr int GT = 32, GN = 64, GK = 32;
+constexpr int GT = 64, GN = 64, GK = 16;
 
 template <typename TW>
 __global__ void __launch_bounds__(256)
@@ -155,16 +155,18 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
                    float decay_scale, float* __restrict__ a_out, float* __restrict__ x_out, int T, int C, int bs) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float Us[GT][GK + 1];
-    __shared__ float Wa[GN][GK + 1];
-    __shared__ float Wi[GN][GK + 1];
+    // tiles stored k-major, so that a thread's four tokens (or channels) of one k are one 16-byte load
+    // (rows padded by four floats: the transposing stores of a warp then spread over eight banks)
+    __shared__ __align__(16) float Us[GK][GT + 4];
+    __shared__ __align__(16) float Wa[GK][GN + 4];
+    __shared__ __align__(16) float Wi[GK][GN + 4];
     const int part = blockIdx.z;
     const int t0 = blockIdx.x * GT, n0 = blockIdx.y * GN;   // n0: first out channel within the part
     const int tid = threadIdx.x;
-    const int tn = tid & 15, tt = tid >> 4;                  // channels tn + 16 j (j < 4), tokens tt + 16 i (i < 2)
-    float acc_a[2][4], acc_i[2][4];
+    const int tn = tid & 15, tt = tid >> 4;                  // channels 4 tn .. 4 tn + 3, tokens 4 tt .. 4 tt + 3
+    float acc_a[4][4], acc_i[4][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc_a[i][j] = acc_i[i][j] = 0.f;
     const TW* wa_p = wa + (size_t)part * bs * bs;
@@ -172,39 +174,40 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
     for (int k0 = 0; k0 < bs; k0 += GK) {
         for (int e = tid; e < GT * GK; e += 256) {
             const int r = e / GK, k = e - r * GK;
-            Us[r][k] = (t0 + r < T && k0 + k < bs) ? u[(size_t)(t0 + r) * u_stride + part * bs + k0 + k] : 0.f;
+            Us[k][r] = (t0 + r < T && k0 + k < bs) ? u[(size_t)(t0 + r) * u_stride + part * bs + k0 + k] : 0.f;
         }
         for (int e = tid; e < GN * GK; e += 256) {
             const int r = e / GK, k = e - r * GK;
             const bool ok = n0 + r < bs && k0 + k < bs;
-            Wa[r][k] = ok ? to_f32<TW>(wa_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
-            Wi[r][k] = ok ? to_f32<TW>(wi_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+            Wa[k][r] = ok ? to_f32<TW>(wa_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+            Wi[k][r] = ok ? to_f32<TW>(wi_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
         }
         __syncthreads();
-#pragma unroll 8
+#pragma unroll
         for (int k = 0; k < GK; ++k) {
-            float uv[2];
+            const float4 uv = *reinterpret_cast<const float4*>(&Us[k][4 * tt]);
+            const float4 va = *reinterpret_cast<const float4*>(&Wa[k][4 * tn]);
+            const float4 vi = *reinterpret_cast<const float4*>(&Wi[k][4 * tn]);
+            const float ur[4] = {uv.x, uv.y, uv.z, uv.w};
+            const float ar[4] = {va.x, va.y, va.z, va.w};
+            const float ir[4] = {vi.x, vi.y, vi.z, vi.w};
 #pragma unroll
-            for (int i = 0; i < 2; ++i) uv[i] = Us[tt + 16 * i][k];
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float va = Wa[tn + 16 * j][k], vi = Wi[tn + 16 * j][k];
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    acc_a[i][j] = fmaf(uv[i], va, acc_a[i][j]);
-                    acc_i[i][j] = fmaf(uv[i], vi, acc_i[i][j]);
+                for (int j = 0; j < 4; ++j) {
+                    acc_a[i][j] = fmaf(ur[i], ar[j], acc_a[i][j]);
+                    acc_i[i][j] = fmaf(ur[i], ir[j], acc_i[i][j]);
                 }
-            }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int t = t0 + tt + 16 * i;
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + 4 * tt + i;
         if (t >= T) continue;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int n = n0 + tn + 16 * j;
+            const int n = n0 + 4 * tn + j;
             if (n >= bs) continue;
             const int c = part * bs + n;
             const float r = 1.0f / (1.0f + expf(-(acc_a[i][j] + ba[c])));
@@ -220,7 +223,8 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
 
 // ------------------------------------------------------------------------------------- the recurrence itself
 // S_t = a_t * S_(t-1) + x_t per channel over the tokens of an entry, from state[slot] and back into it;
-// out[t][c] = S_t * gelu_tanh(y[t][c] + y_bias[c]).  A thread a channel of an entry; loads run four tokens ahead.
+// out[t][c] = S_t * gelu_tanh(y[t][c] + y_bias[c]).  A thread a channel of an entry; the loads of sixteen tokens are
+// in flight at once (none depends on the recurrence).
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
@@ -241,16 +245,17 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
     float S = *sp;
     const float yb = y_bias ? y_bias[c] : 0.f;
     int t = t0;
-    for (; t + 4 <= t1; t += 4) {
-        float av[4], xv[4], yv[4];
+    constexpr int AHEAD = 16;
+    for (; t + AHEAD <= t1; t += AHEAD) {
+        float av[AHEAD], xv[AHEAD], yv[AHEAD];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < AHEAD; ++k) {
             av[k] = a[(size_t)(t + k) * C + c];
             xv[k] = x[(size_t)(t + k) * C + c];
             yv[k] = y[(size_t)(t + k) * y_stride + c];
         }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < AHEAD; ++k) {
             S = fmaf(av[k], S, xv[k]);
             out[(size_t)(t + k) * C + c] = from_f32<TO>(S * gelu_tanh_f(yv[k] + yb));
         }
