@@ -1076,8 +1076,12 @@ def linedra_kernels(hbm_gbs, bf16_tflops, size):
         ba, bi, lam = f32(W), f32(W), f32(W)
         a, xg = torch.empty(T, W, device=dev), torch.empty(T, W, device=dev)
         us = time_kernel(lambda: K.rglru_gates(u, wa, wi, ba, bi, lam, 8.0, a, xg), flush=flush)
+        # beside the framework's exact fp32 product on a shape of the same work: [T, bs] x [2 W, bs]
+        ga, gw, go = f32(T, bs), f32(2 * W, bs), torch.empty(T, 2 * W, device=dev)
+        us_g = time_kernel(lambda: K.gemm_f32(ga, gw, go), flush=flush)
         out[f"recurrent_gates_{tag}"] = {"us": round(us, 1), "fma_frac": round(2 * T * W * bs / (us * 1e-6) / fma_per_s, 4),
-                                         "hbm_frac": frac(T * W * 12 + 2 * W * bs * 2, us)}
+                                         "hbm_frac": frac(T * W * 12 + 2 * W * bs * 2, us),
+                                         "gemm_f32_us": round(us_g, 1), "gemm_f32_fma_frac": round(2 * T * W * bs / (us_g * 1e-6) / fma_per_s, 4)}
         a.uniform_(0.5, 0.99)
         yv, sy = f32(T, W), torch.empty(T, W, device=dev, dtype=torch.bfloat16)
         rstate = torch.zeros(entries + 1, W, device=dev)

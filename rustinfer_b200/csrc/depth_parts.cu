@@ -15,7 +15,26 @@ namespace {
 //   dwa:    v <- sum_{j < n_prev} dwa[j] * hist[j] + dwa[n_prev] * v;   avg_out <- v   (the depth average)
 //   out:    out <- rms(v) * next_w           (the norm before the next sublayer; next_w null: weight 1)
 // rms(x) = x / sqrt(mean(x^2) + eps).  rows: only these rows are read, nothing but `out` is written.
-template <typename TD, typename TO>
+// four elements at a time where rows allow it (V = 4: d and the strides multiples of four, 16-byte aligned pointers)
+template <typename T> __device__ __forceinline__ float4 load4(const T* p);
+template <> __device__ __forceinline__ float4 load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4<bf16>(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const unsigned*>(&lo);
+    u.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+
+template <typename TD, typename TO, int V>
 __global__ void rms_sandwich_kernel(const float* __restrict__ h_in, int in_stride, const TD* __restrict__ delta,
                                     int delta_stride, const float* __restrict__ post_w, float* __restrict__ h_out,
                                     const float* __restrict__ hist, long long layer_stride, int n_prev,
@@ -24,43 +43,94 @@ __global__ void rms_sandwich_kernel(const float* __restrict__ h_in, int in_strid
                                     const int* __restrict__ rows, int d, float eps) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     const float inv_d = 1.0f / (float)d;
     const float* hp = h_in + (size_t)src * in_stride;
+    const int step = blockDim.x * V, first = threadIdx.x * V;
     if (delta) {
         const TD* dp = delta + (size_t)src * delta_stride;
         float q = 0.f;
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            const float v = to_f32<TD>(dp[i]);
-            row[i] = v;
-            q += v * v;
+        for (int i = first; i < d; i += step) {
+            if (V == 4) {
+                const float4 v = load4<TD>(dp + i);
+                *reinterpret_cast<float4*>(row + i) = v;
+                q += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            } else {
+                const float v = to_f32<TD>(dp[i]);
+                row[i] = v;
+                q += v * v;
+            }
         }
         const float inv = 1.0f / sqrtf(block_sum(q, red) * inv_d + eps);
-        for (int i = threadIdx.x; i < d; i += blockDim.x) row[i] = hp[i] + row[i] * inv * post_w[i];
+        for (int i = first; i < d; i += step) {
+            if (V == 4) {
+                const float4 h = load4<float>(hp + i), w = load4<float>(post_w + i);
+                float4 v = *reinterpret_cast<float4*>(row + i);
+                v = make_float4(h.x + v.x * inv * w.x, h.y + v.y * inv * w.y, h.z + v.z * inv * w.z, h.w + v.w * inv * w.w);
+                *reinterpret_cast<float4*>(row + i) = v;
+            } else {
+                row[i] = hp[i] + row[i] * inv * post_w[i];
+            }
+        }
     } else {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) row[i] = hp[i];
+        for (int i = first; i < d; i += step) {
+            if (V == 4) *reinterpret_cast<float4*>(row + i) = load4<float>(hp + i);
+            else row[i] = hp[i];
+        }
     }
+    // (a thread reads back only what it wrote itself, so no barrier is needed between these loops)
     if (h_out && !rows && (delta || h_out != h_in))
-        for (int i = threadIdx.x; i < d; i += blockDim.x) h_out[(size_t)src * d + i] = row[i];
+        for (int i = first; i < d; i += step) {
+            if (V == 4) store4<float>(h_out + (size_t)src * d + i, *reinterpret_cast<float4*>(row + i));
+            else h_out[(size_t)src * d + i] = row[i];
+        }
     if (dwa) {
         const float w_last = dwa[n_prev];
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            float a = 0.f;
-            for (int j = 0; j < n_prev; ++j) a = fmaf(dwa[j], hist[(size_t)j * layer_stride + (size_t)src * d + i], a);
-            a = fmaf(w_last, row[i], a);
-            row[i] = a;
-            if (avg_out && !rows) avg_out[(size_t)src * d + i] = a;
+        for (int i = first; i < d; i += step) {
+            if (V == 4) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < n_prev; ++j) {
+                    const float wj = dwa[j];
+                    const float4 x = load4<float>(hist + (size_t)j * layer_stride + (size_t)src * d + i);
+                    a = make_float4(fmaf(wj, x.x, a.x), fmaf(wj, x.y, a.y), fmaf(wj, x.z, a.z), fmaf(wj, x.w, a.w));
+                }
+                const float4 v = *reinterpret_cast<float4*>(row + i);
+                a = make_float4(fmaf(w_last, v.x, a.x), fmaf(w_last, v.y, a.y), fmaf(w_last, v.z, a.z), fmaf(w_last, v.w, a.w));
+                *reinterpret_cast<float4*>(row + i) = a;
+                if (avg_out && !rows) store4<float>(avg_out + (size_t)src * d + i, a);
+            } else {
+                float a = 0.f;
+                for (int j = 0; j < n_prev; ++j) a = fmaf(dwa[j], hist[(size_t)j * layer_stride + (size_t)src * d + i], a);
+                a = fmaf(w_last, row[i], a);
+                row[i] = a;
+                if (avg_out && !rows) avg_out[(size_t)src * d + i] = a;
+            }
         }
     }
     if (!out) return;
     float q = 0.f;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) q += row[i] * row[i];
+    for (int i = first; i < d; i += step) {
+        if (V == 4) {
+            const float4 v = *reinterpret_cast<float4*>(row + i);
+            q += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        } else {
+            q += row[i] * row[i];
+        }
+    }
     const float inv = 1.0f / sqrtf(block_sum(q, red) * inv_d + eps);
     TO* op = out + (size_t)r * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) op[i] = from_f32<TO>(row[i] * inv * (next_w ? next_w[i] : 1.f));
+    for (int i = first; i < d; i += step) {
+        if (V == 4) {
+            const float4 v = *reinterpret_cast<float4*>(row + i);
+            const float4 w = next_w ? load4<float>(next_w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+            store4<TO>(op + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+        } else {
+            op[i] = from_f32<TO>(row[i] * inv * (next_w ? next_w[i] : 1.f));
+        }
+    }
 }
 
 // ----------------------------------------------------------------------- short causal convolution with a state
@@ -68,9 +138,9 @@ __global__ void rms_sandwich_kernel(const float* __restrict__ h_in, int in_strid
 // y[t][c] = (residual ? x'[t][c] : 0) + bias[c] + sum_j w[c][j] * x'[t - taps + 1 + j][c] over the tokens of one
 // entry; the taps - 1 inputs before the entry's first token come from state[slot] ([taps - 1][C], oldest first;
 // zeros for a new request), and the entry's last taps - 1 inputs go back there.  A thread owns one channel of a
-// chunk of CONV_CHUNK tokens of one entry; the thread of an entry's first chunk is the only one that reads or
+// chunk of CONV_CHUNK tokens of one entry (their loads in flight at once); the thread of an entry's first chunk is the only one that reads or
 // writes the channel's state.
-constexpr int CONV_MAX_TAPS = 8, CONV_CHUNK = 32;
+constexpr int CONV_MAX_TAPS = 8, CONV_CHUNK = 8;
 
 template <typename TI, typename TO>
 __global__ void short_conv_kernel(const TI* __restrict__ x, int x_stride, const float* __restrict__ w,
@@ -102,15 +172,22 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int x_stride, const 
                 old[k] = st[(size_t)(back - 1 - k) * C];
                 win[k] = old[k];
             } else {
-                const int idx = i0 - 1 - k;                  // >= 0: CONV_CHUNK >= taps - 1
+                const int idx = i0 - 1 - k;                  // >= 0: CONV_CHUNK >= CONV_MAX_TAPS - 1
                 win[k] = to_f32<TI>(x[(size_t)(t0 + idx) * x_stride + c]) + ib;
             }
         }
     }
     const float b = bias ? bias[c] : 0.f;
     const int i1 = min(q_len, i0 + CONV_CHUNK);
-    for (int i = i0; i < i1; ++i) {
-        const float cur = to_f32<TI>(x[(size_t)(t0 + i) * x_stride + c]) + ib;
+    float in[CONV_CHUNK];
+#pragma unroll
+    for (int k = 0; k < CONV_CHUNK; ++k)
+        in[k] = i0 + k < i1 ? to_f32<TI>(x[(size_t)(t0 + i0 + k) * x_stride + c]) + ib : 0.f;
+#pragma unroll
+    for (int kk = 0; kk < CONV_CHUNK; ++kk) {
+        const int i = i0 + kk;
+        if (i >= i1) break;
+        const float cur = in[kk];
         float y = b + (residual ? cur : 0.f);
         y = fmaf(wt[back], cur, y);
 #pragma unroll
@@ -144,18 +221,21 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int x_stride, const 
 // u [T][C] fp32 in `blocks` equal parts of bs channels; wa, wi [blocks][bs][bs] ([out][in]), ba, bi [C]:
 //   r = sigmoid(wa[b] u_b + ba),  i = sigmoid(wi[b] u_b + bi),  log a = -decay_scale * r * softplus(lam),
 //   a_out = exp(log a),  x_out = sqrt(1 - a^2) * i * u          (1 - a^2 formed as -expm1(2 log a))
-// A CTA of 256 threads owns GT tokens x GN channels of one part; every sum runs over k = 0, 1, .. in order with
-// fp32 multiply-adds, so a value does not depend on which tokens share its tile.
-constexpr int GT = 64, GN = 64, GK = 16;
+// Every sum runs over k = 0, 1, .. in order with fp32 multiply-adds, so a value does not depend on which tokens share
+// its tile, nor on the tile's size.
+constexpr int GK = 16;
 
-template <typename TW>
+// A CTA of 256 threads (16 x 16) owns 16 TM tokens x 16 TN channels of one part; a thread TM x TN outputs of both
+// matrices.  <4, 4> for many tokens; <1, 2> for a step of few, so that the grid still has CTAs for the SMs.
+template <typename TW, int TM, int TN>
 __global__ void __launch_bounds__(256)
 rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restrict__ wa, const TW* __restrict__ wi,
                    const float* __restrict__ ba, const float* __restrict__ bi, const float* __restrict__ lam,
                    float decay_scale, float* __restrict__ a_out, float* __restrict__ x_out, int T, int C, int bs) {
     pdl_trigger();
     pdl_wait();
-    // tiles stored k-major, so that a thread's four tokens (or channels) of one k are one 16-byte load
+    constexpr int GT = 16 * TM, GN = 16 * TN;
+    // tiles stored k-major, so that a thread's tokens (or channels) of one k lie side by side
     // (rows padded by four floats: the transposing stores of a warp then spread over eight banks)
     __shared__ __align__(16) float Us[GK][GT + 4];
     __shared__ __align__(16) float Wa[GK][GN + 4];
@@ -163,12 +243,12 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
     const int part = blockIdx.z;
     const int t0 = blockIdx.x * GT, n0 = blockIdx.y * GN;   // n0: first out channel within the part
     const int tid = threadIdx.x;
-    const int tn = tid & 15, tt = tid >> 4;                  // channels 4 tn .. 4 tn + 3, tokens 4 tt .. 4 tt + 3
-    float acc_a[4][4], acc_i[4][4];
+    const int tn = tid & 15, tt = tid >> 4;                  // channels TN tn .., tokens TM tt ..
+    float acc_a[TM][TN], acc_i[TM][TN];
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc_a[i][j] = acc_i[i][j] = 0.f;
+        for (int j = 0; j < TN; ++j) acc_a[i][j] = acc_i[i][j] = 0.f;
     const TW* wa_p = wa + (size_t)part * bs * bs;
     const TW* wi_p = wi + (size_t)part * bs * bs;
     for (int k0 = 0; k0 < bs; k0 += GK) {
@@ -185,16 +265,18 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
         __syncthreads();
 #pragma unroll
         for (int k = 0; k < GK; ++k) {
-            const float4 uv = *reinterpret_cast<const float4*>(&Us[k][4 * tt]);
-            const float4 va = *reinterpret_cast<const float4*>(&Wa[k][4 * tn]);
-            const float4 vi = *reinterpret_cast<const float4*>(&Wi[k][4 * tn]);
-            const float ur[4] = {uv.x, uv.y, uv.z, uv.w};
-            const float ar[4] = {va.x, va.y, va.z, va.w};
-            const float ir[4] = {vi.x, vi.y, vi.z, vi.w};
+            float ur[TM], ar[TN], ir[TN];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < TM; ++i) ur[i] = Us[k][TM * tt + i];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < TN; ++j) {
+                ar[j] = Wa[k][TN * tn + j];
+                ir[j] = Wi[k][TN * tn + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
                     acc_a[i][j] = fmaf(ur[i], ar[j], acc_a[i][j]);
                     acc_i[i][j] = fmaf(ur[i], ir[j], acc_i[i][j]);
                 }
@@ -202,12 +284,12 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int t = t0 + 4 * tt + i;
+    for (int i = 0; i < TM; ++i) {
+        const int t = t0 + TM * tt + i;
         if (t >= T) continue;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int n = n0 + 4 * tn + j;
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + TN * tn + j;
             if (n >= bs) continue;
             const int c = part * bs + n;
             const float r = 1.0f / (1.0f + expf(-(acc_a[i][j] + ba[c])));
@@ -223,14 +305,15 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
 
 // ------------------------------------------------------------------------------------- the recurrence itself
 // S_t = a_t * S_(t-1) + x_t per channel over the tokens of an entry, from state[slot] and back into it;
-// out[t][c] = S_t * gelu_tanh(y[t][c] + y_bias[c]).  A thread a channel of an entry; the loads of sixteen tokens are
-// in flight at once (none depends on the recurrence).
+// out[t][c] = S_t * gelu_tanh(y[t][c] + y_bias[c]).  A thread a channel of an entry.  The recurrence itself is one
+// dependent multiply-add a token, so for entries of many tokens the walk does nothing else (the loads of 32 tokens
+// in flight at once, S stored over x) and the gelu and the product run over all tokens at once in a second kernel.
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-template <typename TO>
-__global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __restrict__ x, const float* __restrict__ y,
+template <typename TO, bool FUSED>
+__global__ void rglru_scan_kernel(const float* __restrict__ a, float* __restrict__ x, const float* __restrict__ y,
                                   int y_stride, const float* __restrict__ y_bias, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                                   TO* __restrict__ out, int C) {
@@ -243,28 +326,49 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
     if (t1 <= t0) return;
     float* sp = state + (size_t)state_slots[e] * C + c;
     float S = *sp;
-    const float yb = y_bias ? y_bias[c] : 0.f;
-    int t = t0;
-    constexpr int AHEAD = 16;
-    for (; t + AHEAD <= t1; t += AHEAD) {
-        float av[AHEAD], xv[AHEAD], yv[AHEAD];
-#pragma unroll
-        for (int k = 0; k < AHEAD; ++k) {
-            av[k] = a[(size_t)(t + k) * C + c];
-            xv[k] = x[(size_t)(t + k) * C + c];
-            yv[k] = y[(size_t)(t + k) * y_stride + c];
+    if (FUSED) {
+        // few tokens an entry: S * gelu_tanh(y + b_y) written here
+        const float yb = y_bias ? y_bias[c] : 0.f;
+        for (int t = t0; t < t1; ++t) {
+            S = fmaf(a[(size_t)t * C + c], S, x[(size_t)t * C + c]);
+            out[(size_t)t * C + c] = from_f32<TO>(S * gelu_tanh_f(y[(size_t)t * y_stride + c] + yb));
         }
+    } else {
+        // many tokens: the walk is one multiply-add a token and stores S over x; rglru_finish_kernel does the rest
+        constexpr int AHEAD = 32;
+        int t = t0;
+        for (; t + AHEAD <= t1; t += AHEAD) {
+            float av[AHEAD], xv[AHEAD];
 #pragma unroll
-        for (int k = 0; k < AHEAD; ++k) {
-            S = fmaf(av[k], S, xv[k]);
-            out[(size_t)(t + k) * C + c] = from_f32<TO>(S * gelu_tanh_f(yv[k] + yb));
+            for (int k = 0; k < AHEAD; ++k) {
+                av[k] = a[(size_t)(t + k) * C + c];
+                xv[k] = x[(size_t)(t + k) * C + c];
+            }
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                S = fmaf(av[k], S, xv[k]);
+                x[(size_t)(t + k) * C + c] = S;
+            }
         }
-    }
-    for (; t < t1; ++t) {
-        S = fmaf(a[(size_t)t * C + c], S, x[(size_t)t * C + c]);
-        out[(size_t)t * C + c] = from_f32<TO>(S * gelu_tanh_f(y[(size_t)t * y_stride + c] + yb));
+        for (; t < t1; ++t) {
+            S = fmaf(a[(size_t)t * C + c], S, x[(size_t)t * C + c]);
+            x[(size_t)t * C + c] = S;
+        }
     }
     *sp = S;
+}
+
+// out[t][c] = S[t][c] * gelu_tanh(y[t][c] + y_bias[c])
+template <typename TO>
+__global__ void rglru_finish_kernel(const float* __restrict__ S, const float* __restrict__ y, int y_stride,
+                                    const float* __restrict__ y_bias, TO* __restrict__ out, int T, int C) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)T * C;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / C), c = (int)(i - (long long)t * C);
+        out[i] = from_f32<TO>(S[i] * gelu_tanh_f(y[(size_t)t * y_stride + c] + (y_bias ? y_bias[c] : 0.f)));
+    }
 }
 
 // ----------------------------------------------------------------------------------------- element-wise parts
@@ -308,18 +412,24 @@ RI_API int ri_rms_sandwich(const float* h_in, int in_stride, const void* delta, 
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024 || (delta && !post_w) || (dwa && n_prev > 0 && !hist)) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = d >= 2048 ? 512 : d >= 512 ? 256 : 128;
-#define RI_RS(TD, TO) do { \
+    const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = d % 4 == 0 && in_stride % 4 == 0 && delta_stride % 4 == 0 && layer_stride % 4 == 0 && al(h_in) && al(delta) &&
+                     al(post_w) && al(h_out) && al(hist) && al(avg_out) && al(next_w) && al(out);
+    const int lanes = vec ? d / 4 : d;
+    const int threads = lanes >= 1024 ? 512 : lanes >= 256 ? 256 : lanes >= 128 ? 128 : 64;
+#define RI_RS(TD, TO, V) do { \
         static size_t configured = 48 * 1024; \
         if (smem > configured) { \
-            cudaError_t e = cudaFuncSetAttribute(rms_sandwich_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+            cudaError_t e = cudaFuncSetAttribute(rms_sandwich_kernel<TD, TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
             if (e != cudaSuccess) return (int)e; \
             configured = 200 * 1024; } \
-        RI_CHECKED(ri_launch(rms_sandwich_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, s, h_in, in_stride, \
+        RI_CHECKED(ri_launch(rms_sandwich_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), smem, s, h_in, in_stride, \
             (const TD*)delta, delta_stride, post_w, h_out, hist, layer_stride, n_prev, dwa, avg_out, next_w, (TO*)out, \
             rows, d, eps)); } while (0)
-    if (delta_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_RS(bf16, bf16); else RI_RS(bf16, float); }
-    else { if (out_dtype == RI_BF16) RI_RS(float, bf16); else RI_RS(float, float); }
+#define RI_RS2(TD, TO) do { if (vec) RI_RS(TD, TO, 4); else RI_RS(TD, TO, 1); } while (0)
+    if (delta_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_RS2(bf16, bf16); else RI_RS2(bf16, float); }
+    else { if (out_dtype == RI_BF16) RI_RS2(float, bf16); else RI_RS2(float, float); }
+#undef RI_RS2
 #undef RI_RS
     return ri_launch_status();
 }
@@ -352,30 +462,40 @@ RI_API int ri_rglru_gates(const float* u, int u_stride, const void* wa, const vo
     if (blocks <= 0 || C % blocks) return (int)cudaErrorInvalidValue;
     const int bs = C / blocks;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((T + GT - 1) / GT, (bs + GN - 1) / GN, blocks);
-    if (w_dtype == RI_BF16)
-        RI_CHECKED(ri_launch(rglru_gates_kernel<bf16>, grid, dim3(256), 0, s, u, u_stride, (const bf16*)wa, (const bf16*)wi,
-                             ba, bi, lam, decay_scale, a_out, x_out, T, C, bs));
-    else
-        RI_CHECKED(ri_launch(rglru_gates_kernel<float>, grid, dim3(256), 0, s, u, u_stride, (const float*)wa,
-                             (const float*)wi, ba, bi, lam, decay_scale, a_out, x_out, T, C, bs));
+#define RI_GATES(TW, TM, TN) do { \
+        const dim3 grid((T + 16 * TM - 1) / (16 * TM), (bs + 16 * TN - 1) / (16 * TN), blocks); \
+        RI_CHECKED(ri_launch(rglru_gates_kernel<TW, TM, TN>, grid, dim3(256), 0, s, u, u_stride, (const TW*)wa, (const TW*)wi, \
+                             ba, bi, lam, decay_scale, a_out, x_out, T, C, bs)); } while (0)
+    if (T > 128) { if (w_dtype == RI_BF16) RI_GATES(bf16, 4, 4); else RI_GATES(float, 4, 4); }
+    else { if (w_dtype == RI_BF16) RI_GATES(bf16, 1, 2); else RI_GATES(float, 1, 2); }
+#undef RI_GATES
     return ri_launch_status();
 }
 
-// a, x fp32 [T][C]; y fp32 rows of y_stride; y_bias fp32 [C] or null; state fp32 [slots][C]; out [T][C] of out_dtype
-RI_API int ri_rglru_scan(const float* a, const float* x, const float* y, int y_stride, const float* y_bias, float* state,
+// a, x fp32 [T][C] (x is overwritten); y fp32 rows of y_stride; y_bias fp32 [C] or null; state fp32 [slots][C]; out [T][C]
+// of out_dtype.  max_q_len: an upper bound of the entries' token counts (it picks the one-kernel or the two-kernel form).
+RI_API int ri_rglru_scan(const float* a, float* x, const float* y, int y_stride, const float* y_bias, float* state,
                          const int* cu_q, const int* state_slots, void* out, int out_dtype, int n_entries, int C,
-                         void* stream) {
-    if (n_entries <= 0) return 0;
+                         int T, int max_q_len, void* stream) {
+    if (n_entries <= 0 || T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = C >= 2048 ? 128 : 64;
+    const int threads = 64;
     const dim3 grid((C + threads - 1) / threads, n_entries);
-    if (out_dtype == RI_BF16)
-        RI_CHECKED(ri_launch(rglru_scan_kernel<bf16>, grid, dim3(threads), 0, s, a, x, y, y_stride, y_bias, state, cu_q,
-                             state_slots, (bf16*)out, C));
-    else
-        RI_CHECKED(ri_launch(rglru_scan_kernel<float>, grid, dim3(threads), 0, s, a, x, y, y_stride, y_bias, state, cu_q,
-                             state_slots, (float*)out, C));
+    const bool fused = max_q_len <= 8;
+#define RI_SCAN(TO, F) RI_CHECKED(ri_launch(rglru_scan_kernel<TO, F>, grid, dim3(threads), 0, s, a, x, y, y_stride, y_bias, \
+        state, cu_q, state_slots, (TO*)out, C))
+    if (fused) { if (out_dtype == RI_BF16) RI_SCAN(bf16, true); else RI_SCAN(float, true); }
+    else {
+        if (out_dtype == RI_BF16) RI_SCAN(bf16, false); else RI_SCAN(float, false);
+        const long long total = (long long)T * C;
+        if (out_dtype == RI_BF16)
+            RI_CHECKED(ri_launch(rglru_finish_kernel<bf16>, dim3(ew_blocks(total)), dim3(256), 0, s, (const float*)x, y, y_stride,
+                                 y_bias, (bf16*)out, T, C));
+        else
+            RI_CHECKED(ri_launch(rglru_finish_kernel<float>, dim3(ew_blocks(total)), dim3(256), 0, s, (const float*)x, y, y_stride,
+                                 y_bias, (float*)out, T, C));
+    }
+#undef RI_SCAN
     return ri_launch_status();
 }
 

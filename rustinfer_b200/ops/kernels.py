@@ -666,9 +666,12 @@ def rglru_gates(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.T
 
 
 def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
-               cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int) -> None:
+               cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int,
+               max_q_len: Optional[int] = None) -> None:
     """S_t = a_t * S_(t-1) + x_t per channel over each entry's tokens, from state[slot] (fp32 [slots, C]) and back
-    into it; out[t] = S_t * gelu_tanh(y[t] + y_bias).  a, x fp32 [T, C]; y fp32 [T, C], may be a column view."""
+    into it; out[t] = S_t * gelu_tanh(y[t] + y_bias).  a, x fp32 [T, C] (x is scratch: it may come back holding S);
+    y fp32 [T, C], may be a column view.  `max_q_len`: an upper bound of the entries' token counts (default: T);
+    entries of up to 8 tokens run as one launch, longer ones as a bare walk and an element-wise launch."""
     require_cuda(a, x, y, y_bias, state, cu_q, state_slots, out)
     _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
     T, C = a.shape
@@ -682,8 +685,10 @@ def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Option
         raise KernelError("rglru_scan: state is contiguous fp32 [slots, C]")
     if out.shape != (T, C) or not out.is_contiguous():
         raise KernelError("rglru_scan: out is contiguous [T, C]")
+    mq = T if max_q_len is None else int(max_q_len)
     check(L.core().ri_rglru_scan(_p(a), _p(x), _p(y), y.stride(0), _p(y_bias), _p(state), _p(cu_q), _p(state_slots),
-                                 _p(out), dtype_code(out.dtype), int(n_entries), C, stream_ptr()), "rglru_scan")
+                                 _p(out), dtype_code(out.dtype), int(n_entries), C, T, mq, stream_ptr()), "rglru_scan",
+          1 if mq <= 8 else 2)
 
 
 def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, group: int, out: torch.Tensor) -> None:

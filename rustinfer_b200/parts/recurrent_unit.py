@@ -81,5 +81,5 @@ class GatedRecurrentUnit(Mixer):
         K.rglru_gates(u, self.wa, self.wi, self.ba, self.bi, self.lam, self.decay_scale, a, x)
         sy = torch.empty((T, W), dtype=self.ctx.dtype, device=dev)
         K.rglru_scan(a, x, proj[:, :W], self.y_bias, state_cache.state, step.cu_q, step.state_slots, sy,
-                     step.num_entries)
+                     step.num_entries, step.max_q_len)
         return self.o(sy, out_dtype=torch.float32)

