@@ -251,18 +251,38 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
         for (int j = 0; j < TN; ++j) acc_a[i][j] = acc_i[i][j] = 0.f;
     const TW* wa_p = wa + (size_t)part * bs * bs;
     const TW* wi_p = wi + (size_t)part * bs * bs;
-    for (int k0 = 0; k0 < bs; k0 += GK) {
-        for (int e = tid; e < GT * GK; e += 256) {
-            const int r = e / GK, k = e - r * GK;
-            Us[k][r] = (t0 + r < T && k0 + k < bs) ? u[(size_t)(t0 + r) * u_stride + part * bs + k0 + k] : 0.f;
+    // a tile's elements travel global -> registers -> shared memory; the next tile's loads are in flight while this
+    // one is multiplied
+    constexpr int UL = (GT * GK + 255) / 256, WL = (GN * GK + 255) / 256;
+    float ureg[UL], areg[WL], ireg[WL];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int x = 0; x < UL; ++x) {
+            const int e = tid + 256 * x, r = e / GK, k = e - r * GK;
+            ureg[x] = (e < GT * GK && t0 + r < T && k0 + k < bs) ? u[(size_t)(t0 + r) * u_stride + part * bs + k0 + k] : 0.f;
         }
-        for (int e = tid; e < GN * GK; e += 256) {
-            const int r = e / GK, k = e - r * GK;
-            const bool ok = n0 + r < bs && k0 + k < bs;
-            Wa[k][r] = ok ? to_f32<TW>(wa_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
-            Wi[k][r] = ok ? to_f32<TW>(wi_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+#pragma unroll
+        for (int x = 0; x < WL; ++x) {
+            const int e = tid + 256 * x, r = e / GK, k = e - r * GK;
+            const bool ok = e < GN * GK && n0 + r < bs && k0 + k < bs;
+            areg[x] = ok ? to_f32<TW>(wa_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+            ireg[x] = ok ? to_f32<TW>(wi_p[(size_t)(n0 + r) * bs + k0 + k]) : 0.f;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < bs; k0 += GK) {
+#pragma unroll
+        for (int x = 0; x < UL; ++x) {
+            const int e = tid + 256 * x, r = e / GK, k = e - r * GK;
+            if (e < GT * GK) Us[k][r] = ureg[x];
+        }
+#pragma unroll
+        for (int x = 0; x < WL; ++x) {
+            const int e = tid + 256 * x, r = e / GK, k = e - r * GK;
+            if (e < GN * GK) { Wa[k][r] = areg[x]; Wi[k][r] = ireg[x]; }
         }
         __syncthreads();
+        if (k0 + GK < bs) fetch(k0 + GK);
 #pragma unroll
         for (int k = 0; k < GK; ++k) {
             float ur[TM], ar[TN], ir[TN];
