@@ -223,15 +223,32 @@ __global__ void short_conv_kernel(const TI* __restrict__ x, int x_stride, const 
 //   a_out = exp(log a),  x_out = sqrt(1 - a^2) * i * u          (1 - a^2 formed as -expm1(2 log a))
 // Every sum runs over k = 0, 1, .. in order with fp32 multiply-adds, so a value does not depend on which tokens share
 // its tile, nor on the tile's size.
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 constexpr int GK = 16;
 
 // A CTA of 256 threads (16 x 16) owns 16 TM tokens x 16 TN channels of one part; a thread TM x TN outputs of both
 // matrices.  <4, 4> for many tokens; <1, 2> for a step of few, so that the grid still has CTAs for the SMs.
-template <typename TW, int TM, int TN>
+// What a step of single tokens (token t is entry t) does right in the gates' epilogue instead of storing a and x:
+// S = a * state[slot] + x back into the state, and out = S * gelu_tanh(y + y_bias).
+template <typename TO>
+struct StepTail {
+    float* state;                // [slots][C]; null: store a_out and x_out
+    const int* state_slots;
+    const float* y;
+    int y_stride;
+    const float* y_bias;
+    TO* out;                     // [T][C]
+};
+
+template <typename TW, int TM, int TN, typename TO>
 __global__ void __launch_bounds__(256)
 rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restrict__ wa, const TW* __restrict__ wi,
                    const float* __restrict__ ba, const float* __restrict__ bi, const float* __restrict__ lam,
-                   float decay_scale, float* __restrict__ a_out, float* __restrict__ x_out, int T, int C, int bs) {
+                   float decay_scale, float* __restrict__ a_out, float* __restrict__ x_out, int T, int C, int bs,
+                   StepTail<TO> tail) {
     pdl_trigger();
     pdl_wait();
     constexpr int GT = 16 * TM, GN = 16 * TN;
@@ -317,8 +334,17 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
             const float l = lam[c];
             const float sp = l > 20.f ? l : log1pf(expf(l));
             const float log_a = -decay_scale * r * sp;
-            a_out[(size_t)t * C + c] = expf(log_a);
-            x_out[(size_t)t * C + c] = sqrtf(-expm1f(2.0f * log_a)) * g * u[(size_t)t * u_stride + c];
+            const float av = expf(log_a), xv = sqrtf(-expm1f(2.0f * log_a)) * g * u[(size_t)t * u_stride + c];
+            if (tail.state) {
+                float* sp_ = tail.state + (size_t)tail.state_slots[t] * C + c;
+                const float S = fmaf(av, *sp_, xv);
+                *sp_ = S;
+                tail.out[(size_t)t * C + c] = from_f32<TO>(
+                    S * gelu_tanh_f(tail.y[(size_t)t * tail.y_stride + c] + (tail.y_bias ? tail.y_bias[c] : 0.f)));
+            } else {
+                a_out[(size_t)t * C + c] = av;
+                x_out[(size_t)t * C + c] = xv;
+            }
         }
     }
 }
@@ -328,9 +354,6 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
 // out[t][c] = S_t * gelu_tanh(y[t][c] + y_bias[c]).  A thread a channel of an entry.  The recurrence itself is one
 // dependent multiply-add a token, so for entries of many tokens the walk does nothing else (the loads of 32 tokens
 // in flight at once, S stored over x) and the gelu and the product run over all tokens at once in a second kernel.
-__device__ __forceinline__ float gelu_tanh_f(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
 
 template <typename TO, bool FUSED>
 __global__ void rglru_scan_kernel(const float* __restrict__ a, float* __restrict__ x, const float* __restrict__ y,
@@ -484,11 +507,31 @@ RI_API int ri_rglru_gates(const float* u, int u_stride, const void* wa, const vo
     cudaStream_t s = (cudaStream_t)stream;
 #define RI_GATES(TW, TM, TN) do { \
         const dim3 grid((T + 16 * TM - 1) / (16 * TM), (bs + 16 * TN - 1) / (16 * TN), blocks); \
-        RI_CHECKED(ri_launch(rglru_gates_kernel<TW, TM, TN>, grid, dim3(256), 0, s, u, u_stride, (const TW*)wa, (const TW*)wi, \
-                             ba, bi, lam, decay_scale, a_out, x_out, T, C, bs)); } while (0)
+        RI_CHECKED(ri_launch(rglru_gates_kernel<TW, TM, TN, float>, grid, dim3(256), 0, s, u, u_stride, (const TW*)wa, (const TW*)wi, \
+                             ba, bi, lam, decay_scale, a_out, x_out, T, C, bs, StepTail<float>{})); } while (0)
     if (T > 128) { if (w_dtype == RI_BF16) RI_GATES(bf16, 4, 4); else RI_GATES(float, 4, 4); }
     else { if (w_dtype == RI_BF16) RI_GATES(bf16, 1, 2); else RI_GATES(float, 1, 2); }
 #undef RI_GATES
+    return ri_launch_status();
+}
+
+// A step in which every entry brings one token (token t is entry t, T entries): gates, decay, the recurrence's one
+// step from state[state_slots[t]] and back, and out = S * gelu_tanh(y + y_bias), in one launch.
+RI_API int ri_rglru_step(const float* u, int u_stride, const void* wa, const void* wi, int w_dtype, const float* ba,
+                         const float* bi, const float* lam, float decay_scale, const float* y, int y_stride,
+                         const float* y_bias, float* state, const int* state_slots, void* out, int out_dtype, int T, int C,
+                         int blocks, void* stream) {
+    if (T <= 0) return 0;
+    if (blocks <= 0 || C % blocks || !state || !state_slots) return (int)cudaErrorInvalidValue;
+    const int bs = C / blocks;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid((T + 15) / 16, (bs + 31) / 32, blocks);
+#define RI_STEP(TW, TO) RI_CHECKED(ri_launch(rglru_gates_kernel<TW, 1, 2, TO>, grid, dim3(256), 0, s, u, u_stride, (const TW*)wa, \
+        (const TW*)wi, ba, bi, lam, decay_scale, (float*)nullptr, (float*)nullptr, T, C, bs, \
+        StepTail<TO>{state, state_slots, y, y_stride, y_bias, (TO*)out}))
+    if (w_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_STEP(bf16, bf16); else RI_STEP(bf16, float); }
+    else { if (out_dtype == RI_BF16) RI_STEP(float, bf16); else RI_STEP(float, float); }
+#undef RI_STEP
     return ri_launch_status();
 }
 

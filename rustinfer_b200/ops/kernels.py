@@ -665,6 +665,31 @@ def rglru_gates(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.T
                                   float(decay_scale), _p(a_out), _p(x_out), T, C, blocks, stream_ptr()), "rglru_gates")
 
 
+def rglru_step(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
+               decay_scale: float, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
+               state_slots: torch.Tensor, out: torch.Tensor) -> None:
+    """`rglru_gates` and one step of `rglru_scan` in one launch, for a step in which every entry brings exactly one
+    token (row t of u, y and out is entry t, its state state[state_slots[t]])."""
+    require_cuda(u, wa, wi, ba, bi, lam, y, y_bias, state, state_slots, out)
+    _i32(state_slots, "state_slots")
+    T, C = u.shape
+    blocks = wa.shape[0]
+    if u.dtype != torch.float32 or u.stride(1) != 1 or y.dtype != torch.float32 or y.shape != (T, C) or y.stride(1) != 1:
+        raise KernelError("rglru_step: u and y are fp32 [T, C] with unit column stride")
+    if blocks <= 0 or C % blocks or tuple(wa.shape) != (blocks, C // blocks, C // blocks) or wi.shape != wa.shape \
+            or wi.dtype != wa.dtype or not wa.is_contiguous() or not wi.is_contiguous():
+        raise KernelError("rglru_step: wa and wi are contiguous [blocks, C / blocks, C / blocks] of one dtype")
+    for t, n in ((ba, "ba"), (bi, "bi"), (lam, "lam"), (y_bias, "y_bias")):
+        _f32_vec(t, C, "rglru_step: " + n)
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (C,) or state_slots.numel() < T:
+        raise KernelError("rglru_step: state is contiguous fp32 [slots, C], one slot an entry")
+    if out.shape != (T, C) or not out.is_contiguous():
+        raise KernelError("rglru_step: out is contiguous [T, C]")
+    check(L.core().ri_rglru_step(_p(u), u.stride(0), _p(wa), _p(wi), dtype_code(wa.dtype), _p(ba), _p(bi), _p(lam),
+                                 float(decay_scale), _p(y), y.stride(0), _p(y_bias), _p(state), _p(state_slots), _p(out),
+                                 dtype_code(out.dtype), T, C, blocks, stream_ptr()), "rglru_step")
+
+
 def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
                cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int,
                max_q_len: Optional[int] = None) -> None:

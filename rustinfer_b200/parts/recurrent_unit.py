@@ -76,10 +76,15 @@ class GatedRecurrentUnit(Mixer):
         proj = self.proj(h, out_dtype=torch.float32)                         # [T, 2W]: y, then x
         u = torch.empty((T, W), dtype=torch.float32, device=dev)
         self.conv.run(proj[:, W:], step, conv_cache, u, residual=False, in_bias=self.x_bias)
+        sy = torch.empty((T, W), dtype=self.ctx.dtype, device=dev)
+        if step.max_q_len == 1 and step.num_entries == T:
+            # every entry brings one token: gates, the recurrence's step and the gelu in one launch
+            K.rglru_step(u, self.wa, self.wi, self.ba, self.bi, self.lam, self.decay_scale, proj[:, :W], self.y_bias,
+                         state_cache.state, step.state_slots, sy)
+            return self.o(sy, out_dtype=torch.float32)
         a = torch.empty((T, W), dtype=torch.float32, device=dev)
         x = torch.empty((T, W), dtype=torch.float32, device=dev)
         K.rglru_gates(u, self.wa, self.wi, self.ba, self.bi, self.lam, self.decay_scale, a, x)
-        sy = torch.empty((T, W), dtype=self.ctx.dtype, device=dev)
         K.rglru_scan(a, x, proj[:, :W], self.y_bias, state_cache.state, step.cu_q, step.state_slots, sy,
                      step.num_entries, step.max_q_len)
         return self.o(sy, out_dtype=torch.float32)
