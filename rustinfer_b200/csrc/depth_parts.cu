@@ -241,6 +241,7 @@ struct StepTail {
     int y_stride;
     const float* y_bias;
     TO* out;                     // [T][C]
+    float out_scale;             // a factor on out (a mixer that stands beside another one brings its weight)
 };
 
 template <typename TW, int TM, int TN, typename TO>
@@ -340,7 +341,7 @@ rglru_gates_kernel(const float* __restrict__ u, int u_stride, const TW* __restri
                 const float S = fmaf(av, *sp_, xv);
                 *sp_ = S;
                 tail.out[(size_t)t * C + c] = from_f32<TO>(
-                    S * gelu_tanh_f(tail.y[(size_t)t * tail.y_stride + c] + (tail.y_bias ? tail.y_bias[c] : 0.f)));
+                    tail.out_scale * S * gelu_tanh_f(tail.y[(size_t)t * tail.y_stride + c] + (tail.y_bias ? tail.y_bias[c] : 0.f)));
             } else {
                 a_out[(size_t)t * C + c] = av;
                 x_out[(size_t)t * C + c] = xv;
@@ -359,7 +360,7 @@ template <typename TO, bool FUSED>
 __global__ void rglru_scan_kernel(const float* __restrict__ a, float* __restrict__ x, const float* __restrict__ y,
                                   int y_stride, const float* __restrict__ y_bias, float* __restrict__ state,
                                   const int* __restrict__ cu_q, const int* __restrict__ state_slots,
-                                  TO* __restrict__ out, int C) {
+                                  TO* __restrict__ out, int C, float out_scale) {
     pdl_trigger();
     pdl_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -374,7 +375,7 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, float* __restrict
         const float yb = y_bias ? y_bias[c] : 0.f;
         for (int t = t0; t < t1; ++t) {
             S = fmaf(a[(size_t)t * C + c], S, x[(size_t)t * C + c]);
-            out[(size_t)t * C + c] = from_f32<TO>(S * gelu_tanh_f(y[(size_t)t * y_stride + c] + yb));
+            out[(size_t)t * C + c] = from_f32<TO>(out_scale * S * gelu_tanh_f(y[(size_t)t * y_stride + c] + yb));
         }
     } else {
         // many tokens: the walk is one multiply-add a token and stores S over x; rglru_finish_kernel does the rest
@@ -401,31 +402,31 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, float* __restrict
     *sp = S;
 }
 
-// out[t][c] = S[t][c] * gelu_tanh(y[t][c] + y_bias[c])
+// out[t][c] = out_scale * S[t][c] * gelu_tanh(y[t][c] + y_bias[c])
 template <typename TO>
 __global__ void rglru_finish_kernel(const float* __restrict__ S, const float* __restrict__ y, int y_stride,
-                                    const float* __restrict__ y_bias, TO* __restrict__ out, int T, int C) {
+                                    const float* __restrict__ y_bias, TO* __restrict__ out, int T, int C, float out_scale) {
     pdl_trigger();
     pdl_wait();
     const long long total = (long long)T * C;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / C), c = (int)(i - (long long)t * C);
-        out[i] = from_f32<TO>(S[i] * gelu_tanh_f(y[(size_t)t * y_stride + c] + (y_bias ? y_bias[c] : 0.f)));
+        out[i] = from_f32<TO>(out_scale * S[i] * gelu_tanh_f(y[(size_t)t * y_stride + c] + (y_bias ? y_bias[c] : 0.f)));
     }
 }
 
 // ----------------------------------------------------------------------------------------- element-wise parts
-// out[t][j] = o[t][j] * sigmoid(g[t][j / group]): group 1 a gate a channel, group = a head's width a gate a head
+// out[t][j] = scale * o[t][j] * sigmoid(g[t][j / group]): group 1 a gate a channel, group = a head's width a gate a head
 template <typename TI, typename TO>
 __global__ void sigmoid_gate_kernel(const TI* __restrict__ o, int o_stride, const float* __restrict__ g, int g_stride,
-                                    int group, TO* __restrict__ out, int T, int n) {
+                                    int group, TO* __restrict__ out, int T, int n, float scale) {
     pdl_trigger();
     pdl_wait();
     const long long total = (long long)T * n;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / n), j = (int)(i - (long long)t * n);
         const float gv = g[(size_t)t * g_stride + j / group];
-        out[i] = from_f32<TO>(to_f32<TI>(o[(size_t)t * o_stride + j]) / (1.0f + expf(-gv)));
+        out[i] = from_f32<TO>(scale * to_f32<TI>(o[(size_t)t * o_stride + j]) / (1.0f + expf(-gv)));
     }
 }
 
@@ -520,7 +521,7 @@ RI_API int ri_rglru_gates(const float* u, int u_stride, const void* wa, const vo
 RI_API int ri_rglru_step(const float* u, int u_stride, const void* wa, const void* wi, int w_dtype, const float* ba,
                          const float* bi, const float* lam, float decay_scale, const float* y, int y_stride,
                          const float* y_bias, float* state, const int* state_slots, void* out, int out_dtype, int T, int C,
-                         int blocks, void* stream) {
+                         int blocks, float out_scale, void* stream) {
     if (T <= 0) return 0;
     if (blocks <= 0 || C % blocks || !state || !state_slots) return (int)cudaErrorInvalidValue;
     const int bs = C / blocks;
@@ -528,7 +529,7 @@ RI_API int ri_rglru_step(const float* u, int u_stride, const void* wa, const voi
     const dim3 grid((T + 15) / 16, (bs + 31) / 32, blocks);
 #define RI_STEP(TW, TO) RI_CHECKED(ri_launch(rglru_gates_kernel<TW, 1, 2, TO>, grid, dim3(256), 0, s, u, u_stride, (const TW*)wa, \
         (const TW*)wi, ba, bi, lam, decay_scale, (float*)nullptr, (float*)nullptr, T, C, bs, \
-        StepTail<TO>{state, state_slots, y, y_stride, y_bias, (TO*)out}))
+        StepTail<TO>{state, state_slots, y, y_stride, y_bias, (TO*)out, out_scale}))
     if (w_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_STEP(bf16, bf16); else RI_STEP(bf16, float); }
     else { if (out_dtype == RI_BF16) RI_STEP(float, bf16); else RI_STEP(float, float); }
 #undef RI_STEP
@@ -539,24 +540,24 @@ RI_API int ri_rglru_step(const float* u, int u_stride, const void* wa, const voi
 // of out_dtype.  max_q_len: an upper bound of the entries' token counts (it picks the one-kernel or the two-kernel form).
 RI_API int ri_rglru_scan(const float* a, float* x, const float* y, int y_stride, const float* y_bias, float* state,
                          const int* cu_q, const int* state_slots, void* out, int out_dtype, int n_entries, int C,
-                         int T, int max_q_len, void* stream) {
+                         int T, int max_q_len, float out_scale, void* stream) {
     if (n_entries <= 0 || T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 64;
     const dim3 grid((C + threads - 1) / threads, n_entries);
     const bool fused = max_q_len <= 8;
 #define RI_SCAN(TO, F) RI_CHECKED(ri_launch(rglru_scan_kernel<TO, F>, grid, dim3(threads), 0, s, a, x, y, y_stride, y_bias, \
-        state, cu_q, state_slots, (TO*)out, C))
+        state, cu_q, state_slots, (TO*)out, C, out_scale))
     if (fused) { if (out_dtype == RI_BF16) RI_SCAN(bf16, true); else RI_SCAN(float, true); }
     else {
         if (out_dtype == RI_BF16) RI_SCAN(bf16, false); else RI_SCAN(float, false);
         const long long total = (long long)T * C;
         if (out_dtype == RI_BF16)
             RI_CHECKED(ri_launch(rglru_finish_kernel<bf16>, dim3(ew_blocks(total)), dim3(256), 0, s, (const float*)x, y, y_stride,
-                                 y_bias, (bf16*)out, T, C));
+                                 y_bias, (bf16*)out, T, C, out_scale));
         else
             RI_CHECKED(ri_launch(rglru_finish_kernel<float>, dim3(ew_blocks(total)), dim3(256), 0, s, (const float*)x, y, y_stride,
-                                 y_bias, (float*)out, T, C));
+                                 y_bias, (float*)out, T, C, out_scale));
     }
 #undef RI_SCAN
     return ri_launch_status();
@@ -564,13 +565,13 @@ RI_API int ri_rglru_scan(const float* a, float* x, const float* y, int y_stride,
 
 // o rows of o_stride (RI_F32 or RI_BF16), g fp32 rows of g_stride, out [T][n] of out_dtype
 RI_API int ri_sigmoid_gate(const void* o, int o_dtype, int o_stride, const float* g, int g_stride, int group, void* out,
-                           int out_dtype, int T, int n, void* stream) {
+                           int out_dtype, int T, int n, float scale, void* stream) {
     const long long total = (long long)T * n;
     if (total <= 0) return 0;
     if (group <= 0) return (int)cudaErrorInvalidValue;
     cudaStream_t s = (cudaStream_t)stream;
 #define RI_SG(TI, TO) RI_CHECKED(ri_launch(sigmoid_gate_kernel<TI, TO>, dim3(ew_blocks(total)), dim3(256), 0, s, (const TI*)o, \
-        o_stride, g, g_stride, group, (TO*)out, T, n))
+        o_stride, g, g_stride, group, (TO*)out, T, n, scale))
     if (o_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_SG(bf16, bf16); else RI_SG(bf16, float); }
     else { if (out_dtype == RI_BF16) RI_SG(float, bf16); else RI_SG(float, float); }
 #undef RI_SG

@@ -667,9 +667,9 @@ def rglru_gates(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.T
 
 def rglru_step(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
                decay_scale: float, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
-               state_slots: torch.Tensor, out: torch.Tensor) -> None:
+               state_slots: torch.Tensor, out: torch.Tensor, out_scale: float = 1.0) -> None:
     """`rglru_gates` and one step of `rglru_scan` in one launch, for a step in which every entry brings exactly one
-    token (row t of u, y and out is entry t, its state state[state_slots[t]])."""
+    token (row t of u, y and out is entry t, its state state[state_slots[t]]).  `out_scale`: a factor on out."""
     require_cuda(u, wa, wi, ba, bi, lam, y, y_bias, state, state_slots, out)
     _i32(state_slots, "state_slots")
     T, C = u.shape
@@ -687,16 +687,17 @@ def rglru_step(u: torch.Tensor, wa: torch.Tensor, wi: torch.Tensor, ba: torch.Te
         raise KernelError("rglru_step: out is contiguous [T, C]")
     check(L.core().ri_rglru_step(_p(u), u.stride(0), _p(wa), _p(wi), dtype_code(wa.dtype), _p(ba), _p(bi), _p(lam),
                                  float(decay_scale), _p(y), y.stride(0), _p(y_bias), _p(state), _p(state_slots), _p(out),
-                                 dtype_code(out.dtype), T, C, blocks, stream_ptr()), "rglru_step")
+                                 dtype_code(out.dtype), T, C, blocks, float(out_scale), stream_ptr()), "rglru_step")
 
 
 def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor,
                cu_q: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor, n_entries: int,
-               max_q_len: Optional[int] = None) -> None:
+               max_q_len: Optional[int] = None, out_scale: float = 1.0) -> None:
     """S_t = a_t * S_(t-1) + x_t per channel over each entry's tokens, from state[slot] (fp32 [slots, C]) and back
     into it; out[t] = S_t * gelu_tanh(y[t] + y_bias).  a, x fp32 [T, C] (x is scratch: it may come back holding S);
     y fp32 [T, C], may be a column view.  `max_q_len`: an upper bound of the entries' token counts (default: T);
-    entries of up to 8 tokens run as one launch, longer ones as a bare walk and an element-wise launch."""
+    entries of up to 8 tokens run as one launch, longer ones as a bare walk and an element-wise launch.  `out_scale`:
+    a factor on out."""
     require_cuda(a, x, y, y_bias, state, cu_q, state_slots, out)
     _i32(cu_q, "cu_q"); _i32(state_slots, "state_slots")
     T, C = a.shape
@@ -712,12 +713,12 @@ def rglru_scan(a: torch.Tensor, x: torch.Tensor, y: torch.Tensor, y_bias: Option
         raise KernelError("rglru_scan: out is contiguous [T, C]")
     mq = T if max_q_len is None else int(max_q_len)
     check(L.core().ri_rglru_scan(_p(a), _p(x), _p(y), y.stride(0), _p(y_bias), _p(state), _p(cu_q), _p(state_slots),
-                                 _p(out), dtype_code(out.dtype), int(n_entries), C, T, mq, stream_ptr()), "rglru_scan",
+                                 _p(out), dtype_code(out.dtype), int(n_entries), C, T, mq, float(out_scale), stream_ptr()), "rglru_scan",
           1 if mq <= 8 else 2)
 
 
-def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, group: int, out: torch.Tensor) -> None:
-    """out[t, j] = o[t, j] * sigmoid(gate[t, j // group]): o [T, n], gate fp32 [T, n / group] (both may be column
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, group: int, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, j] = scale * o[t, j] * sigmoid(gate[t, j // group]): o [T, n], gate fp32 [T, n / group] (both may be column
     views).  group 1: a gate a channel; group = a head's width: a gate a head."""
     require_cuda(o, gate, out)
     T, n = o.shape
@@ -726,7 +727,7 @@ def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, group: int, out: torch.Ten
     if out.shape != o.shape or not out.is_contiguous():
         raise KernelError("sigmoid_gate: out is contiguous [T, n]")
     check(L.core().ri_sigmoid_gate(_p(o), dtype_code(o.dtype), o.stride(0), _p(gate), gate.stride(0), int(group), _p(out),
-                                   dtype_code(out.dtype), T, n, stream_ptr()), "sigmoid_gate")
+                                   dtype_code(out.dtype), T, n, float(scale), stream_ptr()), "sigmoid_gate")
 
 
 def softcap(x: torch.Tensor, cap: float) -> None:

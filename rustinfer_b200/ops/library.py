@@ -74,9 +74,9 @@ _SIGNATURES = {
     "ri_rms_sandwich": [_P, _I, _P, _I, _I, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "ri_short_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ri_rglru_gates": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
-    "ri_rglru_step": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "ri_rglru_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
-    "ri_sigmoid_gate": [_P, _I, _I, _P, _I, _I, _P, _I, _I, _I, _P],
+    "ri_rglru_step": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],
+    "ri_rglru_scan": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "ri_sigmoid_gate": [_P, _I, _I, _P, _I, _I, _P, _I, _I, _I, _F, _P],
     "ri_softcap": [_P, _L, _F, _P],
     "ri_glu_pairs": [_P, _P, _I, _L, _I, _F, _F, _P],
     "ri_gated_decay": [_P, _P, _I, _F, _I, _I, _P],

@@ -113,6 +113,16 @@ class PlainAttend:
         return out
 
 
+def project_out(o: Linear, y: torch.Tensor, add_to: Optional[torch.Tensor]) -> torch.Tensor:
+    """y W_o^T in fp32; with `add_to` (fp32 [T, hidden]) added into it (inside the product where the weight can) and
+    `add_to` returned."""
+    if add_to is None:
+        return o(y, out_dtype=torch.float32)
+    if not o.add_into(y, add_to):
+        K.residual_add(add_to, o(y, out_dtype=torch.float32))
+    return add_to
+
+
 def _shared_position(ctx: BuildContext, spec: Optional[PartSpec]):
     if spec is None:
         return None
@@ -368,8 +378,11 @@ class DistanceBiasAttention(Mixer):
     holds exp(sink_h), a learned number per head with no key or value), head_gate (head h's output is multiplied
     by sigmoid of the h-th of H numbers W_g x), tensor_names.  Tensors: q, k, v, o, and `sink` [H], `g` [H, hidden]
     where asked for; no biases.  q, k, v and the gates are one product of the input; scores, softmax weights and
-    their product with the values are fp32 in both engines (the kernels `PlainAttend` picks)."""
+    their product with the values are fp32 in both engines (the kernels `PlainAttend` picks).  Beside another mixer
+    (`parallel_mixers`) it takes the joint product's columns as `proj`, and with a gate a head an `out_scale` on what
+    its output product reads and an `add_to` that product is added into."""
     graph_safe = True
+    joins_input = True
 
     def __init__(self, params):
         super().__init__(params)
@@ -387,6 +400,7 @@ class DistanceBiasAttention(Mixer):
         if not (1 <= self.hd <= 512 and 1 <= self.vd <= 512):
             raise ValueError(f"head sizes {self.hd}, {self.vd}: the attention kernel takes sizes up to 512")
         self.nq, self.nk, self.nv = self.H * self.hd, self.G * self.hd, self.G * self.vd
+        self.scales_output = self.head_gate          # the gate's kernel is where a factor on the output is free
 
     def _name(self, local: str) -> str:
         return self.tensor_names.get(local, local)
@@ -421,10 +435,12 @@ class DistanceBiasAttention(Mixer):
         self.o = Linear(tensors[n("o")], self.ctx.num_sms)
         self.sink_values = tensors[n("sink")].to(torch.float32).contiguous() if self.sink else None
 
-    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache, proj: Optional[torch.Tensor] = None,
+                out_scale: float = 1.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
         T, dt = x.shape[0], self.ctx.dtype
         g = step.groups[cache.group]
-        proj = self.proj(x, out_dtype=torch.float32)
+        if proj is None:
+            proj = self.proj(x, out_dtype=torch.float32)
         nqkv = self.nq + self.nk + self.nv
         q = torch.empty((T, self.nq), dtype=dt, device=x.device)
         K.qkv_prepare(proj[:, :nqkv], None, None, None, 0, 0.0, step.positions, None, None, 0, False,
@@ -434,8 +450,10 @@ class DistanceBiasAttention(Mixer):
             o = torch.empty((T, self.H * self.vd), dtype=torch.float32, device=x.device)
             self.attend(q, o, step, cache, self.scale, sink_values=self.sink_values, slopes=self.slopes)
             y = torch.empty((T, self.H * self.vd), dtype=dt, device=x.device)
-            K.sigmoid_gate(o, proj[:, nqkv:], self.vd, y)
+            K.sigmoid_gate(o, proj[:, nqkv:], self.vd, y, scale=out_scale)
         else:
+            if out_scale != 1.0:
+                raise ValueError("a factor on the output rides on the heads' gate; this mixer has none")
             y = torch.empty((T, self.H * self.vd), dtype=dt, device=x.device)
             self.attend(q, y, step, cache, self.scale, sink_values=self.sink_values, slopes=self.slopes)
-        return self.o(y, out_dtype=torch.float32)
+        return project_out(self.o, y, add_to)

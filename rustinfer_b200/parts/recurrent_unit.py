@@ -10,16 +10,18 @@ Recurrences with Local Attention for Efficient Language Models"): two branches o
 The state S (fp32, zero for a new request) and the convolution's last taps - 1 inputs sit in slots of two
 fixed-state cache groups.  The projections are matrix products of the engine's precision with fp32 results; the
 convolution, the gates' products, the decay, the recurrence and the gelu are fp32 in both engines, and S * y is
-rounded once for the output product.  The reference engine has no recurrent mixer
+rounded once for the output product.  Beside another mixer (`parallel_mixers`) the part takes the joint product's
+columns as `proj`, an `out_scale` on S * y and an `add_to` its output product is added into.  The reference engine has no recurrent mixer
 (crates/infer-worker/src/components/attention.rs is its only one).
 """
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
 from ..ops import kernels as K
+from .attention_variants import project_out
 from .base import BuildContext, FixedState, Mixer, ParamDecl, StepContext, register_mixer
 from .linear import Linear
 from .short_conv import ConvState
@@ -32,6 +34,8 @@ class GatedRecurrentUnit(Mixer):
     [blocks, width/blocks, width/blocks] ([out, in]) with biases ra.b, ri.b [blocks, width/blocks]; lam [width];
     o [hidden, width]."""
     graph_safe = True
+    joins_input = True
+    scales_output = True
 
     def __init__(self, params):
         super().__init__(params)
@@ -70,21 +74,23 @@ class GatedRecurrentUnit(Mixer):
         self.ba, self.bi, self.lam = f32("ra.b"), f32("ri.b"), f32("lam")
         self.o = Linear(tensors[n("o")], self.ctx.num_sms)
 
-    def forward(self, h: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, step: StepContext, cache, proj: Optional[torch.Tensor] = None,
+                out_scale: float = 1.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
         conv_cache, state_cache = cache
         T, W, dev = h.shape[0], self.width, h.device
-        proj = self.proj(h, out_dtype=torch.float32)                         # [T, 2W]: y, then x
+        if proj is None:
+            proj = self.proj(h, out_dtype=torch.float32)                     # [T, 2W]: y, then x
         u = torch.empty((T, W), dtype=torch.float32, device=dev)
         self.conv.run(proj[:, W:], step, conv_cache, u, residual=False, in_bias=self.x_bias)
         sy = torch.empty((T, W), dtype=self.ctx.dtype, device=dev)
         if step.max_q_len == 1 and step.num_entries == T:
             # every entry brings one token: gates, the recurrence's step and the gelu in one launch
             K.rglru_step(u, self.wa, self.wi, self.ba, self.bi, self.lam, self.decay_scale, proj[:, :W], self.y_bias,
-                         state_cache.state, step.state_slots, sy)
-            return self.o(sy, out_dtype=torch.float32)
+                         state_cache.state, step.state_slots, sy, out_scale)
+            return project_out(self.o, sy, add_to)
         a = torch.empty((T, W), dtype=torch.float32, device=dev)
         x = torch.empty((T, W), dtype=torch.float32, device=dev)
         K.rglru_gates(u, self.wa, self.wi, self.ba, self.bi, self.lam, self.decay_scale, a, x)
         K.rglru_scan(a, x, proj[:, :W], self.y_bias, state_cache.state, step.cu_q, step.state_slots, sy,
-                     step.num_entries, step.max_q_len)
-        return self.o(sy, out_dtype=torch.float32)
+                     step.num_entries, step.max_q_len, out_scale)
+        return project_out(self.o, sy, add_to)
