@@ -34,13 +34,39 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float4 v) {
     *reinterpret_cast<uint2*>(p) = u;
 }
 
+// A short causal convolution on the normed output, for a step in which row r is the one token of entry r:
+// out <- n + sum_j w[c][j] * n_(t - taps + 1 + j) with the earlier inputs from state[slots[r]] ([taps - 1][d], oldest
+// first), which is shifted by the new input.  w null: none.
+struct ConvTail {
+    const float* w;              // [d][taps]
+    float* state;                // [slots][taps - 1][d]
+    const int* slots;
+    int taps;
+};
+
+template <typename TO>
+__device__ __forceinline__ float conv_tail(const ConvTail& ct, int r, int c, int d, float n) {
+    const int back = ct.taps - 1;
+    const float* wc = ct.w + (size_t)c * ct.taps;
+    float* st = ct.state + (size_t)ct.slots[r] * back * d + c;
+    float y = fmaf(wc[back], n, n);
+    float prev = n;                                          // what row k is overwritten with, walking from the newest
+    for (int k = back - 1; k >= 0; --k) {
+        const float old = st[(size_t)k * d];
+        y = fmaf(wc[k], old, y);
+        st[(size_t)k * d] = prev;
+        prev = old;
+    }
+    return y;
+}
+
 template <typename TD, typename TO, int V>
 __global__ void rms_sandwich_kernel(const float* __restrict__ h_in, int in_stride, const TD* __restrict__ delta,
                                     int delta_stride, const float* __restrict__ post_w, float* __restrict__ h_out,
                                     const float* __restrict__ hist, long long layer_stride, int n_prev,
                                     const float* __restrict__ dwa, float* __restrict__ avg_out,
                                     const float* __restrict__ next_w, TO* __restrict__ out,
-                                    const int* __restrict__ rows, int d, float eps) {
+                                    const int* __restrict__ rows, int d, float eps, ConvTail ct) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float row[];
@@ -126,9 +152,15 @@ __global__ void rms_sandwich_kernel(const float* __restrict__ h_in, int in_strid
         if (V == 4) {
             const float4 v = *reinterpret_cast<float4*>(row + i);
             const float4 w = next_w ? load4<float>(next_w + i) : make_float4(1.f, 1.f, 1.f, 1.f);
-            store4<TO>(op + i, make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w));
+            float4 n = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w);
+            if (ct.w)
+                n = make_float4(conv_tail<TO>(ct, r, i, d, n.x), conv_tail<TO>(ct, r, i + 1, d, n.y),
+                                conv_tail<TO>(ct, r, i + 2, d, n.z), conv_tail<TO>(ct, r, i + 3, d, n.w));
+            store4<TO>(op + i, n);
         } else {
-            op[i] = from_f32<TO>(row[i] * inv * (next_w ? next_w[i] : 1.f));
+            float n = row[i] * inv * (next_w ? next_w[i] : 1.f);
+            if (ct.w) n = conv_tail<TO>(ct, r, i, d, n);
+            op[i] = from_f32<TO>(n);
         }
     }
 }
@@ -447,14 +479,18 @@ inline int ew_blocks(long long n) {
 
 // h_in fp32 rows of in_stride; delta (may be null) rows of delta_stride, RI_F32 or RI_BF16; post_w, next_w, dwa
 // fp32; h_out, avg_out fp32 [rows][d] (each may be null); hist: n_prev earlier results, layer_stride floats apart;
-// out (may be null) [n_rows][d] of out_dtype; rows (may be null): gather, nothing but out is written.
+// out (may be null) [n_rows][d] of out_dtype; rows (may be null): gather, nothing but out is written.  conv_w (may be
+// null) fp32 [d][conv_taps] with conv_state fp32 [slots][conv_taps - 1][d] and conv_slots [n_rows]: see ConvTail.
 RI_API int ri_rms_sandwich(const float* h_in, int in_stride, const void* delta, int delta_dtype, int delta_stride,
                            const float* post_w, float* h_out, const float* hist, long long layer_stride, int n_prev,
                            const float* dwa, float* avg_out, const float* next_w, void* out, int out_dtype,
-                           const int* rows, int n_rows, int d, float eps, void* stream) {
+                           const int* rows, int n_rows, int d, float eps, const float* conv_w, float* conv_state,
+                           const int* conv_slots, int conv_taps, void* stream) {
     if (n_rows <= 0) return 0;
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 200 * 1024 || (delta && !post_w) || (dwa && n_prev > 0 && !hist)) return (int)cudaErrorInvalidValue;
+    if (conv_w && (rows || !out || !conv_slots || conv_taps < 1 || (conv_taps > 1 && !conv_state))) return (int)cudaErrorInvalidValue;
+    const ConvTail ct{conv_w, conv_state, conv_slots, conv_taps};
     cudaStream_t s = (cudaStream_t)stream;
     const auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     const bool vec = d % 4 == 0 && in_stride % 4 == 0 && delta_stride % 4 == 0 && layer_stride % 4 == 0 && al(h_in) && al(delta) &&
@@ -469,7 +505,7 @@ RI_API int ri_rms_sandwich(const float* h_in, int in_stride, const void* delta, 
             configured = 200 * 1024; } \
         RI_CHECKED(ri_launch(rms_sandwich_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), smem, s, h_in, in_stride, \
             (const TD*)delta, delta_stride, post_w, h_out, hist, layer_stride, n_prev, dwa, avg_out, next_w, (TO*)out, \
-            rows, d, eps)); } while (0)
+            rows, d, eps, ct)); } while (0)
 #define RI_RS2(TD, TO) do { if (vec) RI_RS(TD, TO, 4); else RI_RS(TD, TO, 1); } while (0)
     if (delta_dtype == RI_BF16) { if (out_dtype == RI_BF16) RI_RS2(bf16, bf16); else RI_RS2(bf16, float); }
     else { if (out_dtype == RI_BF16) RI_RS2(float, bf16); else RI_RS2(float, float); }

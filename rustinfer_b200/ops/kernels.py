@@ -579,7 +579,8 @@ def _f32_vec(t: Optional[torch.Tensor], n: int, name: str) -> None:
 def rms_sandwich(h_in: torch.Tensor, delta: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
                  h_out: Optional[torch.Tensor], next_w: Optional[torch.Tensor], out: Optional[torch.Tensor], eps: float,
                  rows: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None, n_prev: int = 0,
-                 dwa: Optional[torch.Tensor] = None, avg_out: Optional[torch.Tensor] = None) -> None:
+                 dwa: Optional[torch.Tensor] = None, avg_out: Optional[torch.Tensor] = None,
+                 conv: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> None:
     """RMS norms around a sublayer and the weighted depth average, one launch; v is a row of h_in (fp32 [T, d],
     rows may be a column view):
         delta given:  v += rms(delta) * post_w;   h_out given: h_out <- v;
@@ -587,8 +588,10 @@ def rms_sandwich(h_in: torch.Tensor, delta: Optional[torch.Tensor], post_w: Opti
         out given:    out <- rms(v) * next_w (None: 1)
     with rms(x) = x / sqrt(mean(x^2) + eps).  Weights are fp32 (whatever a model adds to or multiplies into them is
     the caller's business); history is fp32 [layers, T, d].  `rows` (int32): only those rows are read and only
-    `out` is written."""
-    require_cuda(h_in, delta, post_w, h_out, next_w, out, rows, history, dwa, avg_out)
+    `out` is written.  `conv` (weight fp32 [d, taps], state fp32 [slots, taps - 1, d], state_slots int32 [T]), for a
+    step in which row t is the one token of entry t: out <- n + conv(n) as `short_conv` with `residual` computes it,
+    the earlier inputs from state[state_slots[t]], which the new input is shifted into."""
+    require_cuda(h_in, delta, post_w, h_out, next_w, out, rows, history, dwa, avg_out, *(conv or ()))
     _i32(rows, "rows")
     T, d = h_in.shape
     if h_in.dtype != torch.float32 or h_in.stride(1) != 1:
@@ -607,11 +610,20 @@ def rms_sandwich(h_in: torch.Tensor, delta: Optional[torch.Tensor], post_w: Opti
     n_rows = T if rows is None else rows.numel()
     if out is not None and (out.shape != (n_rows, d) or not out.is_contiguous()):
         raise KernelError("rms_sandwich: out is contiguous [rows, d]")
+    cw = cs = cslots = None
+    taps = 0
+    if conv is not None:
+        cw, cs, cslots = conv
+        taps = cw.shape[1]
+        _i32(cslots, "conv slots")
+        if rows is not None or out is None or cw.dtype != torch.float32 or cw.shape[0] != d or not cw.is_contiguous() \
+                or cs.dtype != torch.float32 or not cs.is_contiguous() or tuple(cs.shape[1:]) != (taps - 1, d) or cslots.numel() < T:
+            raise KernelError("rms_sandwich: conv is (fp32 [d, taps], fp32 [slots, taps - 1, d], int32 [T]) and goes with out, without rows")
     check(L.core().ri_rms_sandwich(_p(h_in), h_in.stride(0), _p(delta), dtype_code(delta.dtype) if delta is not None else 0,
                                    delta.stride(0) if delta is not None else 0, _p(post_w), _p(h_out), _p(history),
                                    T * d, int(n_prev), _p(dwa), _p(avg_out), _p(next_w), _p(out),
                                    dtype_code(out.dtype) if out is not None else 0, _p(rows), n_rows, d, float(eps),
-                                   stream_ptr()), "rms_sandwich")
+                                   _p(cw), _p(cs), _p(cslots), int(taps), stream_ptr()), "rms_sandwich")
 
 
 def short_conv_max_taps() -> int:

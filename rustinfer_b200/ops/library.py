@@ -71,7 +71,7 @@ _SIGNATURES = {
     "ri_scaled_sum": [_P, _P, _F, _F, _P, _I, _L, _P],
     "ri_gated_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     "ri_delta_scan": [_P, _I, _P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
-    "ri_rms_sandwich": [_P, _I, _P, _I, _I, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "ri_rms_sandwich": [_P, _I, _P, _I, _I, _P, _P, _P, _L, _I, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P, _P, _P, _I, _P],
     "ri_short_conv": [_P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "ri_rglru_gates": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _P, _I, _I, _I, _P],
     "ri_rglru_step": [_P, _I, _P, _P, _I, _P, _P, _P, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P],

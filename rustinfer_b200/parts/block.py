@@ -9,6 +9,7 @@ crates/infer-core/src/component.rs:8-27).  h is fp32; pending is in the activati
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable, Dict, Optional
 
@@ -147,6 +148,9 @@ def _post_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
     hidden.act = x
 
 
+_FUSE_INPUT_CONV = os.environ.get("RUSTINFER_B200_FUSE_INPUT_CONV", "1") != "0"
+
+
 @dataclass
 class DepthPending:
     """The end of a layer of the `sandwich_depth_average` arrangement that has not run yet: the last sublayer's
@@ -163,10 +167,10 @@ class DepthPending:
     avg_out: torch.Tensor
     eps: float
 
-    def run(self, next_w: Optional[torch.Tensor], out: Optional[torch.Tensor]) -> None:
+    def run(self, next_w: Optional[torch.Tensor], out: Optional[torch.Tensor], conv=None) -> None:
         from ..ops import kernels as K
         K.rms_sandwich(self.h_in, self.delta, self.post_w, self.result, next_w, out, self.eps, history=self.history,
-                       n_prev=self.n_prev, dwa=self.weights, avg_out=self.avg_out)
+                       n_prev=self.n_prev, dwa=self.weights, avg_out=self.avg_out, conv=conv)
 
 
 def settle_depth(hidden: Hidden) -> torch.Tensor:
@@ -199,10 +203,18 @@ def _sandwich_depth_average(block: Block, hidden: Hidden, step: StepContext, cac
     if avg.count != n + 1:
         raise ValueError(f"the layer's depth_average has {avg.count} weights; {n + 1} results exist after it")
     x_in = hidden.stream
-    want = torch.float32 if getattr(block.mixer, "input_float32", False) else None
-    x = block.mixer_norm.add_norm(x_in, hidden.pending, out_dtype=want)
-    hidden.pending = None
-    y = block.mixer.forward(x, step, cache)
+    # a mixer behind a short convolution (`conv_input`), in a step of single tokens: the convolution runs in the norm's
+    # launch and the mixer is told that its input has passed it
+    conv = getattr(block.mixer, "input_conv", None) if _FUSE_INPUT_CONV else None
+    if conv is not None and conv.bias is None and step.max_q_len == 1 and step.num_entries == step.num_tokens:
+        x = block.mixer_norm.add_norm(x_in, hidden.pending, conv=(conv.weight, cache[0].state, step.state_slots))
+        hidden.pending = None
+        y = block.mixer.forward(x, step, cache, conv_done=True)
+    else:
+        want = torch.float32 if getattr(block.mixer, "input_float32", False) else None
+        x = block.mixer_norm.add_norm(x_in, hidden.pending, out_dtype=want)
+        hidden.pending = None
+        y = block.mixer.forward(x, step, cache)
     result = hidden.history[n]
     if block.ffn is None:
         last_in, last_y, last_post = x_in, y, post_mixer

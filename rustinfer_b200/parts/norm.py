@@ -49,29 +49,32 @@ class RMSNorm(Norm):
             self._weight32 = self.weight.to(torch.float32).contiguous()
         return self._weight32
 
-    def add_norm(self, h, delta, rows=None, out_dtype=None):
+    def add_norm(self, h, delta, rows=None, out_dtype=None, conv=None):
+        """`conv` (weight, state, state slots), in a step of single tokens: the short convolution that follows this norm
+        runs in the norm's launch (see `kernels.rms_sandwich`)."""
         from .block import DepthPending
         n = h.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=h.device)
         if isinstance(delta, DepthPending):
             if rows is None and delta.eps == self.eps:
-                delta.run(self.weight32, out)
+                delta.run(self.weight32, out, conv)
             else:
                 delta.run(None, None)
-                K.rms_sandwich(delta.avg_out, None, None, None, self.weight32, out, self.eps, rows=rows)
+                K.rms_sandwich(delta.avg_out, None, None, None, self.weight32, out, self.eps, rows=rows, conv=conv)
             return out
         if isinstance(delta, NormedDelta):
             post = delta.norm
             if rows is None and post.eps == self.eps:
-                K.rms_sandwich(h, delta.delta, post.weight32, h, self.weight32, out, self.eps)
+                K.rms_sandwich(h, delta.delta, post.weight32, h, self.weight32, out, self.eps, conv=conv)
             else:
                 post.add_into(h, delta.delta)
-                K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows)
+                K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows, conv=conv)
             return out
-        if self.weight.dtype == torch.float32 and (delta is None or delta.dtype != out.dtype or self.ctx.dtype != out.dtype):
+        if conv is not None or (self.weight.dtype == torch.float32
+                                and (delta is None or delta.dtype != out.dtype or self.ctx.dtype != out.dtype)):
             if delta is not None:
                 K.residual_add(h, delta)
-            K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows)
+            K.rms_sandwich(h, None, None, None, self.weight32, out, self.eps, rows=rows, conv=conv)
             return out
         K.add_rmsnorm(h, delta, self.weight, self.eps, out, rows)
         return out

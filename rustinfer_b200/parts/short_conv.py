@@ -83,10 +83,19 @@ class ConvInput(Mixer):
         pre = self.inner_prefix
         self.inner.load({n: tensors[pre + n] for n in self.inner.param_decls() if pre + n in tensors})
 
-    def forward(self, x: torch.Tensor, step: StepContext, cache) -> torch.Tensor:
+    @property
+    def input_conv(self) -> ConvState:
+        """The convolution, for a block that can run it in the launch of the norm before it (it then calls
+        `forward(..., conv_done=True)` with x + conv(x) in the activation dtype)."""
+        return self.conv
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache, conv_done: bool = False) -> torch.Tensor:
         caches = list(cache)
-        out = torch.empty(x.shape, dtype=self.ctx.dtype, device=x.device)
-        self.conv.run(x, step, caches[0], out, residual=True)
+        if conv_done:
+            out = x
+        else:
+            out = torch.empty(x.shape, dtype=self.ctx.dtype, device=x.device)
+            self.conv.run(x, step, caches[0], out, residual=True)
         rest = caches[1:]
         inner_cache = None if not rest else rest[0] if self._inner_single else tuple(rest)
         return self.inner.forward(out, step, inner_cache)

@@ -77,6 +77,28 @@ def test_rms_sandwich(d, ddtype):
     assert rel_err(out, P.rms_norm(want, nw.to(F64), eps)) < 1e-6
 
 
+@pytest.mark.parametrize("d,taps", [(96, 4), (83, 2), (64, 1), (1032, 3)])
+def test_rms_sandwich_with_the_convolution(d, taps):
+    """A step of single tokens: the norm's launch also runs the convolution that follows it, from each entry's state
+    slot and back into it; three such steps in a row against the plain convolution over the three tokens."""
+    B, eps = 5, 1e-5
+    slots = [4, 0, 2, 5, 1]
+    w, nw = rnd(d, taps, seed=1, scale=0.5), rnd(d, seed=2)
+    state = torch.zeros(7, taps - 1, d, device=DEV)
+    state[[3, 6]] = float("nan")
+    hs = [rnd(B, d, seed=10 + s) for s in range(3)]
+    outs = []
+    for h in hs:
+        out = torch.empty(B, d, device=DEV)
+        K().rms_sandwich(h.to(DEV), None, None, None, nw.to(DEV), out, eps, conv=(w.to(DEV), state, i32(slots)))
+        outs.append(out.cpu())
+    for b in range(B):
+        n = P.rms_norm(torch.stack([h[b] for h in hs]).to(F64), nw.to(F64), eps)
+        want = n + P.causal_conv(n, w.to(F64))
+        assert rel_err(torch.stack([o[b] for o in outs]), want) < 1e-6, b
+    assert bool(torch.isnan(state[[3, 6]]).all()) or taps == 1
+
+
 def _pieces(T, cuts):
     out, at = [], 0
     while at < T:
