@@ -1103,14 +1103,6 @@ def linedra_kernels(hbm_gbs, bf16_tflops, size):
         us_n = time_kernel(lambda: K.row_norm_gate(o32, g32, wn, 1e-6, y16), flush=flush)
         out[f"head_gate_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(T * ah * av * (4 + 2), us),
                                    "row_norm_gate_us": round(us_n, 1), "row_norm_gate_hbm_frac": frac(T * ah * av * (4 + 4 + 2), us_n)}
-        # the clamped pairs of the experts' first product where it leaves in fp32
-        N, ff = T * sz["top"], sz["expert_ff"]
-        pairs, mid = f32(N, 2 * ff), torch.empty(N, ff, device=dev, dtype=torch.bfloat16)
-        us = time_kernel(lambda: K.glu_pairs(pairs, mid, (7.0, 1.702)), flush=flush)
-        gu16, mid2 = bf(N, 2 * ff), torch.empty(N, ff, device=dev, dtype=torch.bfloat16)
-        us_s = time_kernel(lambda: K.silu_mul(gu16, mid2), flush=flush)
-        out[f"clamped_pairs_{tag}"] = {"us": round(us, 1), "hbm_frac": frac(N * ff * (8 + 2), us),
-                                       "silu_mul_us": round(us_s, 1), "silu_mul_hbm_frac": frac(N * ff * (4 + 2), us_s)}
     # attention with the distance bias beside the same kernels without it (Pikalix's attention with a sink and a window)
     B, ctx, win = 64, 4096, sz["window"]
     nblk = ctx // PAGE

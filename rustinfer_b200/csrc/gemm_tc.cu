@@ -99,7 +99,19 @@ struct Params {
     // skipped by every role alike.  null: one matrix for all rows.
     const int* grp_offsets;
     int grp_experts, grp_tiles_b;
+    // EPI_SILU with glu_limit > 0: the pair (gate g, up u) becomes g' sigmoid(glu_alpha g') (u' + 1) with
+    // g' = min(g, glu_limit), u' = clamp(u, -glu_limit, glu_limit) instead of silu(g) u
+    float glu_limit = 0.f, glu_alpha = 0.f;
 };
+
+__device__ __forceinline__ float glu_mul(const Params& p, float g, float u) {
+    if (p.glu_limit > 0.f) {
+        g = fminf(g, p.glu_limit);
+        u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+        return __fdividef(g, 1.0f + __expf(-p.glu_alpha * g)) * (u + 1.0f);
+    }
+    return silu_mul(g, u);
+}
 
 // Tile `tile` of a grouped product: first row and end of its group's rows, row of B its columns start at,
 // first feature.  False: there is no such tile.
@@ -134,7 +146,7 @@ __device__ __forceinline__ void store_one(const Params& p, int n_tok, int n_feat
         case EPI_RESIDUAL: atomicAdd(reinterpret_cast<float*>(p.out) + row + feat, acc); break;   // parts of one sum may come from several CTAs
         case EPI_SILU:                                   // even feature = gate_j, odd = up_j
             if ((feat & 1) == 0)
-                reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] = __float2bfloat16_rn(silu_mul(acc, neighbour));
+                reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] = __float2bfloat16_rn(glu_mul(p, acc, neighbour));
             break;
     }
 }
@@ -185,7 +197,7 @@ __device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0,
         case EPI_SILU: {
             float m[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) m[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+            for (int j = 0; j < 8; ++j) m[j] = glu_mul(p, v[2 * j], v[2 * j + 1]);
             *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + (feat0 >> 1)) = pack8(m);
             break;
         }
@@ -236,7 +248,7 @@ __device__ __forceinline__ void store_row64(const Params& p, int tok, int feat0,
             for (int q = 0; q < 4; ++q) {
                 float m[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) m[j] = silu_mul(v[16 * q + 2 * j], v[16 * q + 2 * j + 1]);
+                for (int j = 0; j < 8; ++j) m[j] = glu_mul(p, v[16 * q + 2 * j], v[16 * q + 2 * j + 1]);
                 dst[q] = pack8(m);
             }
             break;
@@ -1106,8 +1118,9 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
 // it), W [experts][N][K] bf16.  out [rows][ld_out]: EPI_F32 or EPI_BF16 store X_e W_e^T; EPI_SILU stores
 // silu(gate) * up of matrices whose rows alternate gate_j, up_j into [rows][N / 2].  The grid covers
 // ceil(rows / 128) + experts row tiles; tiles that do not exist are skipped.
+// glu_limit > 0 with EPI_SILU: the clamped pair (see Params) instead of silu(gate) * up.
 RI_API int ri_gemm_tc_grouped(const void* X, const void* W, int rows, int N, int K, void* out, int ld_out, int epilogue,
-                              const int* offsets, int experts, int* error, void* stream) {
+                              const int* offsets, int experts, int* error, float glu_limit, float glu_alpha, void* stream) {
     if (rows <= 0 || N <= 0 || experts <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || !error || !offsets || (epilogue != EPI_F32 && epilogue != EPI_BF16 && epilogue != EPI_SILU) ||
         (epilogue == EPI_SILU && N % 2))
@@ -1121,6 +1134,7 @@ RI_API int ri_gemm_tc_grouped(const void* X, const void* W, int rows, int N, int
     p.splits = 1; p.workspace = nullptr; p.counters = nullptr; p.error = error;
     const int bn = N >= 256 ? 256 : N > 64 ? 128 : N > 32 ? 64 : N > 16 ? 32 : 16;
     p.grp_offsets = offsets; p.grp_experts = experts; p.grp_tiles_b = (N + bn - 1) / bn;
+    p.glu_limit = epilogue == EPI_SILU && glu_limit > 0.f ? glu_limit : 0.f; p.glu_alpha = glu_alpha;
     p.tiles_a = (rows + BM - 1) / BM + experts;
     p.n_tiles = p.tiles_a * p.grp_tiles_b;
     const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU) ? 2 : 4;

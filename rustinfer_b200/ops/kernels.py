@@ -1023,11 +1023,12 @@ def gemm_tc_grouped_supports(rows: int, n: int, k: int) -> bool:
     return k % 8 == 0 and n % 8 == 0
 
 
-def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, epilogue: int) -> None:
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, epilogue: int,
+                    act: Optional[Tuple[float, float]] = None) -> None:
     """Rows in groups against a matrix per group on the tcgen05 tensor cores: x [rows, K] bf16 holds the groups one
     after the other (group e: rows offsets[e] .. offsets[e+1]-1, int32 on the device), w [E, N, K] bf16.  EPI_F32 /
     EPI_BF16 store into out [rows, N]; EPI_SILU stores silu(gate) * up of matrices whose rows alternate gate_j, up_j
-    into out [rows, N/2]."""
+    into out [rows, N/2], or with `act` (limit, alpha) the clamped pair g' sigmoid(alpha g') (u' + 1)."""
     require_cuda(x, w, out, offsets)
     _contig(x, "x"); _contig(w, "w"); _contig(out, "out"); _i32(offsets, "offsets")
     E, N, Kd = w.shape
@@ -1039,8 +1040,11 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets
             or epilogue not in (EPI_BF16, EPI_F32, EPI_SILU)):
         raise KernelError(f"gemm_tc_grouped: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} {out.dtype}")
     err = gemm_tc_state(x.device)[2]
+    if act is not None and epilogue != EPI_SILU:
+        raise KernelError("gemm_tc_grouped: the clamped pair is a form of the gated epilogue")
     check(L.gemm_tc().ri_gemm_tc_grouped(_p(x), _p(w), rows, N, Kd, _p(out), out.stride(0), int(epilogue), _p(offsets), E,
-                                         _p(err), stream_ptr()), "gemm_tc_grouped")
+                                         _p(err), float(act[0]) if act else 0.0, float(act[1]) if act else 0.0,
+                                         stream_ptr()), "gemm_tc_grouped")
 
 
 def moe_combine(Y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],

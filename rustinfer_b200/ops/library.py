@@ -60,7 +60,7 @@ _SIGNATURES = {
     "ri_moe_sort": [_P, _P, _I, _I, _P, _P, _P, _P],
     "ri_moe_product": [_P, _I, _I, _P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "ri_moe_gather": [_P, _P, _I, _P, _I, _I, _P],
-    "ri_gemm_tc_grouped": [_P, _P, _I, _I, _I, _P, _I, _I, _P, _I, _P, _P],
+    "ri_gemm_tc_grouped": [_P, _P, _I, _I, _I, _P, _I, _I, _P, _I, _P, _F, _F, _P],
     "ri_moe_combine": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _I, _P],
     "ri_attention_single_supports": [_I, _I],
     "ri_embed_sinusoid": [_P, _P, _P, _I, _P, _P, _I, _I, _I, _P],

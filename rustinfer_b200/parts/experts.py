@@ -145,12 +145,7 @@ class RoutedExperts(FeedForward):
             # tiles of 128 rows that never cross from one expert's rows into the next one's results
             xs = torch.empty((N, self.hidden), dtype=torch.bfloat16, device=dev)
             K.moe_gather(xin, order, self.top, xs)
-            if self.act is None:
-                K.gemm_tc_grouped(xs, self.gate_up, mid, offsets, K.EPI_SILU)
-            else:                                          # the pairs leave the product in fp32; a kernel of its own clamps them
-                pairs = torch.empty((N, 2 * self.ff), dtype=torch.float32, device=dev)
-                K.gemm_tc_grouped(xs, self.gate_up, pairs, offsets, K.EPI_F32)
-                K.glu_pairs(pairs, mid, self.act)
+            K.gemm_tc_grouped(xs, self.gate_up, mid, offsets, K.EPI_SILU, act=self.act)
             K.gemm_tc_grouped(mid, self.down, Y, offsets, K.EPI_F32)
         else:
             K.moe_product(xin, self.gate_up, mid, offsets, order, self.top, gated=True, act=self.act)
